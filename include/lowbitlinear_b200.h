@@ -1,0 +1,107 @@
+/*
+ * lowbitlinear_b200 -- C ABI of the B200 (sm_100a) W4A16 linear kernels.
+ *
+ * Computes  Y[M,N] = fp16( X[M,K] . dequant(W)[N,K]^T )  for weights stored as group-64
+ * asymmetric INT4:
+ *   packed_w  int32 [N, ceil(K/8)]   eight unsigned nibbles per word, low nibble first
+ *   scales    float [N, ceil(K/64)]
+ *   zeros     int32 [N, ceil(K/64)]  zero points in 0..15
+ *   w[n,k] = (q[n,k] - zeros[n,k/64]) * scales[n,k/64]
+ * X and Y are IEEE binary16, row-major and dense.  All pointers are device pointers on
+ * `device`; nothing is retained after a call returns; no call synchronises the host.
+ *
+ * Every function returns LBL_OK (0) or a negative code and then leaves a message that
+ * lbl_last_error() returns to the same host thread.
+ *
+ * The entry points replace the two launchers of the reference extension
+ * (NanjinLin/LowBitLinear):
+ *   lbl_w4a16_gemv  <-  w4a16_gemv_warp_vec_launcher   csrc/w4a16_gemv_warp_vec.cu:111-195
+ *   lbl_w4a16_gemm  <-  cute_w4a16_gemm_launcher       csrc/cute_w4a16_gemm.cu:190-248
+ * Tensor allocation, dtype/shape/contiguity checks and exception text stay with the host
+ * binding, as TORCH_CHECK does for the reference.
+ */
+#ifndef LOWBITLINEAR_B200_H_
+#define LOWBITLINEAR_B200_H_
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define LBL_OK 0
+#define LBL_ERR_INVALID (-1)     /* null pointer, bad size or misaligned buffer            */
+#define LBL_ERR_CUDA (-2)        /* a CUDA runtime call or the launch itself failed         */
+#define LBL_ERR_WORKSPACE (-3)   /* workspace missing or smaller than lbl_w4a16_workspace_bytes */
+#define LBL_ERR_UNSUPPORTED (-4) /* forced path cannot serve this shape                     */
+#define LBL_ERR_DEVICE_WAIT (-5) /* a bounded device-side wait expired (see lbl_device_status) */
+
+/* Kernel paths.  LBL_PATH_AUTO lets the size-based dispatcher choose. */
+#define LBL_PATH_AUTO 0
+#define LBL_PATH_GENERIC 1      /* masked any-shape kernel (plain loads, FP32 FMA)          */
+#define LBL_PATH_GEMV 2         /* streaming skinny kernel, M <= 32, one pass over K        */
+#define LBL_PATH_GEMV_SPLITK 3  /* same kernel, K split across CTAs, ordered reduction      */
+#define LBL_PATH_GEMM_TC 4      /* TMA + tcgen05 tensor-core GEMM, FP32 accumulators in TMEM */
+
+/* Flags. */
+#define LBL_FLAG_PDL 1u            /* programmatic dependent launch: weights are prefetched
+                                      before the previous kernel in the stream has finished.
+                                      Only set it when that kernel does not write the weights. */
+#define LBL_FLAG_ROUND_WEIGHTS 2u  /* generic kernel: round each dequantised weight to FP16
+                                      before the multiply (the reference GEMM's operand policy,
+                                      csrc/cute_w4a16_gemm.cu:160-162)                        */
+
+/* Library version: major * 10000 + minor * 100 + patch. */
+int lbl_version(void);
+
+/* Message of the last failing call made by the calling thread ("" if none). */
+const char* lbl_last_error(void);
+
+/* Path the dispatcher takes for this problem.  `op` is 0 for the M = 1 operator
+ * (FP32 dequantisation) and 1 for the any-shape operator. */
+int lbl_w4a16_select_path(int64_t M, int64_t N, int64_t K, int op);
+
+/* Bytes of scratch the given path (or LBL_PATH_AUTO) needs for this problem; 0 if none.
+ * The scratch holds split-K partial sums followed by one arrival counter per row tile.
+ * The counters must be zero before the first call that uses the buffer
+ * (lbl_w4a16_workspace_init) and every call leaves them zero again, so one buffer can be
+ * reused by successive calls on the same stream. */
+size_t lbl_w4a16_workspace_bytes(int64_t M, int64_t N, int64_t K, int path);
+
+/* Zero a scratch buffer on `stream` (asynchronous). */
+int lbl_w4a16_workspace_init(void* workspace, size_t workspace_bytes, int device, void* stream);
+
+/* y[1,N] = fp16( x[1,K] . dequant(W)^T ), FP32 dequantisation and accumulation.
+ * Requires group_size == 64, K > 0, K % 64 == 0, N > 0, x 16-byte aligned -- the contract of
+ * the reference's w4a16_gemv_warp_vec_launcher (csrc/w4a16_gemv_warp_vec.cu:111-195). */
+int lbl_w4a16_gemv(const void* x, const int32_t* packed_w, const float* scales,
+                   const int32_t* zeros, void* y, int64_t N, int64_t K, int group_size,
+                   void* workspace, size_t workspace_bytes, unsigned flags, int device,
+                   void* stream);
+
+/* Y[M,N] for any M, N, K >= 0 (empty outputs are a no-op; K == 0 writes zeros) -- the
+ * contract of the reference's cute_w4a16_gemm_launcher (csrc/cute_w4a16_gemm.cu:190-248). */
+int lbl_w4a16_gemm(const void* X, const int32_t* packed_w, const float* scales,
+                   const int32_t* zeros, void* Y, int64_t M, int64_t N, int64_t K,
+                   void* workspace, size_t workspace_bytes, unsigned flags, int device,
+                   void* stream);
+
+/* The dispatcher itself: `path` forces a kernel (LBL_ERR_UNSUPPORTED if it cannot serve the
+ * shape) or is LBL_PATH_AUTO; `op` selects the numeric policy as in lbl_w4a16_select_path;
+ * `path_taken`, when not null, receives the path that ran.  The reference has no counterpart:
+ * its choice is made in Python (lowbitlinear/linear.py:100-121). */
+int lbl_w4a16_linear(const void* X, const int32_t* packed_w, const float* scales,
+                     const int32_t* zeros, void* Y, int64_t M, int64_t N, int64_t K, int op,
+                     int path, void* workspace, size_t workspace_bytes, unsigned flags,
+                     int device, void* stream, int* path_taken);
+
+/* Reads (and clears) the device-side status word of `device`: 0, or a code left by a
+ * kernel whose bounded wait on a barrier expired.  Synchronises the device. */
+int lbl_device_status(int device, int* status);
+
+#ifdef __cplusplus
+}
+#endif
+
+#endif /* LOWBITLINEAR_B200_H_ */

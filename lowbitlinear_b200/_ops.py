@@ -1,0 +1,226 @@
+"""ctypes binding of the C ABI and the two torch operators built on it.
+
+The reference registers its operators from C++ (``csrc/w4a16_gemv_warp_vec.cu:197-207``,
+``csrc/cute_w4a16_gemm.cu:250-257``) and checks its arguments with ``TORCH_CHECK``
+(``w4a16_gemv_warp_vec.cu:118-165``, ``cute_w4a16_gemm.cu:196-223``).  Here the same schemas
+are registered with ``torch.library`` for the CUDA dispatch key only, the same checks run in
+the same order and raise ``RuntimeError`` with the same key phrases, the output is allocated
+by torch, and the work is one call into the C ABI on the caller's current stream.  CPU
+tensors never reach this code: the dispatcher raises ``NotImplementedError`` for them, as it
+does for the reference.
+"""
+import ctypes
+import threading
+
+import torch
+
+PATH_AUTO, PATH_GENERIC, PATH_GEMV, PATH_GEMV_SPLITK, PATH_GEMM_TC = range(5)
+PATH_NAMES = {
+    PATH_AUTO: "auto",
+    PATH_GENERIC: "generic",
+    PATH_GEMV: "gemv",
+    PATH_GEMV_SPLITK: "gemv_splitk",
+    PATH_GEMM_TC: "gemm_tc",
+}
+FLAG_PDL = 1
+FLAG_ROUND_WEIGHTS = 2
+
+GEMV_SCHEMA = (
+    "w4a16_gemv_warp_vec(Tensor x, Tensor packed_w, Tensor scales, Tensor zeros, "
+    "int group_size) -> Tensor"
+)
+GEMM_SCHEMA = "gemm(Tensor X, Tensor packed_w, Tensor scales, Tensor zeros) -> Tensor"
+
+_lib = None
+_registered = []  # keeps the torch.library.Library objects alive
+_flags = 0
+_workspaces = {}
+_workspace_lock = threading.Lock()
+
+
+def bind(path):
+    """Open the shared object and declare every entry point of ``lowbitlinear_b200.h``."""
+    global _lib
+    lib = ctypes.CDLL(path)
+    p, i64, i32, u32, sz = (ctypes.c_void_p, ctypes.c_int64, ctypes.c_int, ctypes.c_uint,
+                            ctypes.c_size_t)
+    lib.lbl_version.restype = i32
+    lib.lbl_version.argtypes = []
+    lib.lbl_last_error.restype = ctypes.c_char_p
+    lib.lbl_last_error.argtypes = []
+    lib.lbl_w4a16_select_path.restype = i32
+    lib.lbl_w4a16_select_path.argtypes = [i64, i64, i64, i32]
+    lib.lbl_w4a16_workspace_bytes.restype = sz
+    lib.lbl_w4a16_workspace_bytes.argtypes = [i64, i64, i64, i32]
+    lib.lbl_w4a16_workspace_init.restype = i32
+    lib.lbl_w4a16_workspace_init.argtypes = [p, sz, i32, p]
+    lib.lbl_w4a16_gemv.restype = i32
+    lib.lbl_w4a16_gemv.argtypes = [p, p, p, p, p, i64, i64, i32, p, sz, u32, i32, p]
+    lib.lbl_w4a16_gemm.restype = i32
+    lib.lbl_w4a16_gemm.argtypes = [p, p, p, p, p, i64, i64, i64, p, sz, u32, i32, p]
+    lib.lbl_w4a16_linear.restype = i32
+    lib.lbl_w4a16_linear.argtypes = [p, p, p, p, p, i64, i64, i64, i32, i32, p, sz, u32, i32, p,
+                                     ctypes.POINTER(ctypes.c_int)]
+    lib.lbl_device_status.restype = i32
+    lib.lbl_device_status.argtypes = [i32, ctypes.POINTER(ctypes.c_int)]
+    _lib = lib
+    return lib
+
+
+def set_programmatic_dependent_launch(enabled):
+    """Let consecutive decode kernels overlap: a kernel starts fetching its weights while the
+    previous kernel in the stream is still finishing, and only its activation read waits.
+
+    Safe whenever the kernel that precedes a linear in the stream does not write that linear's
+    weights -- true for inference, where weights are written once.  Off by default."""
+    global _flags
+    _flags = (_flags | FLAG_PDL) if enabled else (_flags & ~FLAG_PDL)
+
+
+def _check(rc):
+    if rc != 0:
+        raise RuntimeError(_lib.lbl_last_error().decode() or f"lowbitlinear_b200 error {rc}")
+
+
+def _workspace(device, stream, m, n, k, path=PATH_AUTO):
+    """Scratch for split-K, cached per (device, stream): zeroed when created, and every kernel
+    leaves its counters zero again."""
+    need = _lib.lbl_w4a16_workspace_bytes(m, n, k, path)
+    if need == 0:
+        return None, 0
+    key = (device.index, stream)
+    with _workspace_lock:
+        buf = _workspaces.get(key)
+        if buf is None or buf.numel() < need:
+            buf = torch.zeros(max(need, 1 << 20), dtype=torch.uint8, device=device)
+            _workspaces[key] = buf
+    return buf.data_ptr(), buf.numel()
+
+
+def device_status(device=None):
+    """Reads and clears the device status word (0 unless a bounded device-side wait expired)."""
+    index = torch.cuda.current_device() if device is None else torch.device(device).index
+    value = ctypes.c_int(0)
+    _check(_lib.lbl_device_status(index, ctypes.byref(value)))
+    return value.value
+
+
+def _require(condition, message):
+    if not condition:
+        raise RuntimeError(message)
+
+
+def w4a16_gemv_warp_vec(x, packed_w, scales, zeros, group_size):
+    """``y[1, N] = fp16(x[1, K] . dequant(W)^T)``, FP32 dequantisation and accumulation."""
+    _require(x.is_cuda, "x must be CUDA")
+    _require(x.dim() == 2 and x.size(0) == 1, "Expected x shape [1, K]")
+    _require(x.dtype == torch.float16, "x must be FP16")
+    _require(packed_w.dtype == torch.int32, "packed_w must be int32")
+    _require(scales.dtype == torch.float32, "scales must be FP32")
+    _require(zeros.dtype == torch.int32, "zeros must be int32")
+    _require(
+        x.is_contiguous() and packed_w.is_contiguous() and scales.is_contiguous()
+        and zeros.is_contiguous(),
+        "All tensors must be contiguous",
+    )
+    _require(packed_w.is_cuda and scales.is_cuda and zeros.is_cuda, "All tensors must be CUDA")
+    _require(
+        x.device == packed_w.device == scales.device == zeros.device,
+        "All tensors must be on the same GPU",
+    )
+    k = x.size(1)
+    _require(
+        group_size == 64 and k > 0 and k % 64 == 0,
+        "Expected group_size=64 and K divisible by 64",
+    )
+    _require(packed_w.dim() == 2, "packed_w must be 2D")
+    n = packed_w.size(0)
+    _require(0 < n <= 2**31 - 1 and k <= 2**31 - 1, "Invalid N or K")
+    _require(packed_w.size(1) == k // 8, "Invalid packed weight shape")
+    _require(
+        tuple(scales.shape) == (n, k // 64) and zeros.shape == scales.shape,
+        "Invalid scales or zeros shape",
+    )
+    _require(x.data_ptr() % 16 == 0, "x must be 16-byte aligned for vector loads")
+
+    y = torch.empty((1, n), dtype=torch.float16, device=x.device)
+    stream = torch.cuda.current_stream(x.device).cuda_stream
+    ws, ws_bytes = _workspace(x.device, stream, 1, n, k)
+    _check(_lib.lbl_w4a16_gemv(x.data_ptr(), packed_w.data_ptr(), scales.data_ptr(),
+                               zeros.data_ptr(), y.data_ptr(), n, k, group_size, ws, ws_bytes,
+                               _flags, x.device.index, stream))
+    return y
+
+
+def w4a16_gemm(X, packed_w, scales, zeros):
+    """``Y[M, N] = fp16(X[M, K] . dequant(W)^T)`` for any M, N, K >= 0, group size 64."""
+    _require(
+        X.is_cuda and packed_w.is_cuda and scales.is_cuda and zeros.is_cuda,
+        "all tensors must be CUDA tensors",
+    )
+    _require(
+        X.device == packed_w.device == scales.device == zeros.device,
+        "all tensors must be on the same GPU",
+    )
+    _require(X.dtype == torch.float16, "X must be float16")
+    _require(packed_w.dtype == torch.int32, "packed_w must be int32")
+    _require(scales.dtype == torch.float32, "scales must be float32")
+    _require(zeros.dtype == torch.int32, "zeros must be int32")
+    _require(
+        X.dim() == 2 and packed_w.dim() == 2 and scales.dim() == 2 and zeros.dim() == 2,
+        "all tensors must be 2D",
+    )
+    _require(
+        X.is_contiguous() and packed_w.is_contiguous() and scales.is_contiguous()
+        and zeros.is_contiguous(),
+        "all tensors must be contiguous",
+    )
+    m, k = X.shape
+    n = packed_w.size(0)
+    _require(packed_w.size(1) == (k + 7) // 8, "packed_w must have shape [N, ceil(K/8)]")
+    groups = (k + 63) // 64
+    _require(tuple(scales.shape) == (n, groups), "scales must have shape [N, ceil(K/64)]")
+    _require(tuple(zeros.shape) == (n, groups), "zeros must have shape [N, ceil(K/64)]")
+
+    Y = torch.empty((m, n), dtype=torch.float16, device=X.device)
+    if m == 0 or n == 0:
+        return Y
+    stream = torch.cuda.current_stream(X.device).cuda_stream
+    ws, ws_bytes = _workspace(X.device, stream, m, n, k) if k > 0 else (None, 0)
+    _check(_lib.lbl_w4a16_gemm(X.data_ptr(), packed_w.data_ptr(), scales.data_ptr(),
+                               zeros.data_ptr(), Y.data_ptr(), m, n, k, ws, ws_bytes, _flags,
+                               X.device.index, stream))
+    return Y
+
+
+def linear_forced(X, packed_w, scales, zeros, path, op=1, flags=None):
+    """Runs the dispatcher with a forced kernel path (benchmarks and tests).  Returns
+    ``(Y, path_taken)``; no argument checking beyond what the C ABI does."""
+    m, k = X.shape
+    n = packed_w.size(0)
+    Y = torch.empty((m, n), dtype=torch.float16, device=X.device)
+    stream = torch.cuda.current_stream(X.device).cuda_stream
+    ws, ws_bytes = _workspace(X.device, stream, m, n, k, path)
+    taken = ctypes.c_int(0)
+    _check(_lib.lbl_w4a16_linear(X.data_ptr(), packed_w.data_ptr(), scales.data_ptr(),
+                                 zeros.data_ptr(), Y.data_ptr(), m, n, k, op, path, ws, ws_bytes,
+                                 _flags if flags is None else flags, X.device.index, stream,
+                                 ctypes.byref(taken)))
+    return Y, taken.value
+
+
+def select_path(m, n, k, op=1):
+    return _lib.lbl_w4a16_select_path(m, n, k, op)
+
+
+def register_operators(lib):
+    """Define the reference's two operator schemas and implement them for CUDA tensors."""
+    if _registered:
+        return
+    ext = torch.library.Library("lowbitlinear_ext", "FRAGMENT")
+    ext.define(GEMV_SCHEMA)
+    ext.impl("w4a16_gemv_warp_vec", w4a16_gemv_warp_vec, "CUDA")
+    cute = torch.library.Library("lowbitlinear_cute_w4a16", "FRAGMENT")
+    cute.define(GEMM_SCHEMA)
+    cute.impl("gemm", w4a16_gemm, "CUDA")
+    _registered.extend((ext, cute))

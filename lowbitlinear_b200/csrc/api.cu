@@ -1,0 +1,314 @@
+// C ABI of the library (declared in include/lowbitlinear_b200.h): argument checks, the
+// size-based dispatcher, scratch layout and the per-device status word.
+#include "../../include/lowbitlinear_b200.h"
+
+#include "kernels.h"
+
+#include <cstdarg>
+#include <cstdio>
+#include <cstdlib>
+#include <mutex>
+
+namespace {
+
+constexpr int kVersion = 100;  // 0.1.0
+constexpr int kMaxDevices = 64;
+
+thread_local char g_error[512] = "";
+
+int fail(int code, const char* fmt, ...) {
+  va_list args;
+  va_start(args, fmt);
+  std::vsnprintf(g_error, sizeof(g_error), fmt, args);
+  va_end(args);
+  return code;
+}
+
+int fail_cuda(cudaError_t err, const char* what) {
+  return fail(LBL_ERR_CUDA, "%s: %s", what, cudaGetErrorString(err));
+}
+
+// One status word per device; kernels with bounded waits report through it.
+__device__ int g_device_status = 0;
+
+struct DeviceInfo {
+  bool ready = false;
+  int sm_count = 0;
+  int* status_word = nullptr;
+};
+DeviceInfo g_devices[kMaxDevices];
+std::mutex g_devices_mutex;
+
+// Makes `device` current for the scope and restores the previous one.
+class DeviceScope {
+ public:
+  explicit DeviceScope(int device) {
+    ok_ = cudaGetDevice(&previous_) == cudaSuccess;
+    if (ok_ && previous_ != device) {
+      ok_ = cudaSetDevice(device) == cudaSuccess;
+      switched_ = ok_;
+    }
+  }
+  ~DeviceScope() {
+    if (switched_) cudaSetDevice(previous_);
+  }
+  bool ok() const { return ok_; }
+
+ private:
+  int previous_ = 0;
+  bool ok_ = false;
+  bool switched_ = false;
+};
+
+// Requires `device` to be current.
+int device_info(int device, DeviceInfo* out) {
+  if (device < 0 || device >= kMaxDevices) return fail(LBL_ERR_INVALID, "device %d out of range", device);
+  std::lock_guard<std::mutex> lock(g_devices_mutex);
+  DeviceInfo& info = g_devices[device];
+  if (!info.ready) {
+    cudaError_t err = cudaDeviceGetAttribute(&info.sm_count, cudaDevAttrMultiProcessorCount, device);
+    if (err != cudaSuccess) return fail_cuda(err, "cudaDeviceGetAttribute");
+    int major = 0;
+    err = cudaDeviceGetAttribute(&major, cudaDevAttrComputeCapabilityMajor, device);
+    if (err != cudaSuccess) return fail_cuda(err, "cudaDeviceGetAttribute");
+    if (major != 10) {
+      return fail(LBL_ERR_UNSUPPORTED, "device %d has compute capability %d.x; this library is built for sm_100a only", device, major);
+    }
+    void* ptr = nullptr;
+    err = cudaGetSymbolAddress(&ptr, g_device_status);
+    if (err != cudaSuccess) return fail_cuda(err, "cudaGetSymbolAddress");
+    info.status_word = static_cast<int*>(ptr);
+    info.ready = true;
+  }
+  *out = info;
+  return LBL_OK;
+}
+
+bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
+
+int forced_path_from_env() {
+  const char* v = std::getenv("LBL_FORCE_PATH");
+  if (v == nullptr || *v == '\0') return LBL_PATH_AUTO;
+  return std::atoi(v);
+}
+
+// Crossover between the streaming kernel and the tensor-core GEMM.
+int tc_min_m() {
+  const char* v = std::getenv("LBL_TC_MIN_M");
+  if (v == nullptr || *v == '\0') return 17;
+  return std::atoi(v);
+}
+
+int select_path(int64_t M, int64_t N, int64_t K, int op, int sm_count) {
+  (void)op;
+  if (M <= 0 || N <= 0 || K <= 0) return LBL_PATH_GENERIC;
+  const bool skinny_ok = lbl::skinny_supports(M, N, K);
+  const bool tc_ok = lbl::gemm_tc_supports(M, N, K);
+  if (tc_ok && (M >= tc_min_m() || !skinny_ok)) return LBL_PATH_GEMM_TC;
+  if (skinny_ok) {
+    lbl::SkinnyPlan plan;
+    if (lbl::skinny_make_plan(M, N, K, -1, sm_count, &plan)) {
+      return plan.nsplit > 1 ? LBL_PATH_GEMV_SPLITK : LBL_PATH_GEMV;
+    }
+  }
+  return LBL_PATH_GENERIC;
+}
+
+int run_linear(const void* X, const int32_t* packed_w, const float* scales, const int32_t* zeros,
+               void* Y, int64_t M, int64_t N, int64_t K, int op, int path, void* workspace,
+               size_t workspace_bytes, unsigned flags, int device, void* stream, int* path_taken) {
+  if (M < 0 || N < 0 || K < 0) return fail(LBL_ERR_INVALID, "negative dimension (M=%lld N=%lld K=%lld)", (long long)M, (long long)N, (long long)K);
+  if (path_taken != nullptr) *path_taken = LBL_PATH_AUTO;
+  if (M == 0 || N == 0) return LBL_OK;  // empty output
+  if (Y == nullptr) return fail(LBL_ERR_INVALID, "Y is null");
+  cudaStream_t cu_stream = static_cast<cudaStream_t>(stream);
+
+  DeviceScope scope(device);
+  if (!scope.ok()) return fail(LBL_ERR_CUDA, "cannot make device %d current", device);
+  DeviceInfo info;
+  const int rc = device_info(device, &info);
+  if (rc != LBL_OK) return rc;
+
+  if (K == 0) {
+    const cudaError_t err = cudaMemsetAsync(Y, 0, static_cast<size_t>(M) * N * sizeof(__half), cu_stream);
+    if (err != cudaSuccess) return fail_cuda(err, "cudaMemsetAsync");
+    return LBL_OK;
+  }
+  if (X == nullptr || packed_w == nullptr || scales == nullptr || zeros == nullptr) {
+    return fail(LBL_ERR_INVALID, "null tensor pointer");
+  }
+
+  lbl::Problem prob;
+  prob.x = static_cast<const __half*>(X);
+  prob.packed = reinterpret_cast<const uint32_t*>(packed_w);
+  prob.scales = scales;
+  prob.zeros = zeros;
+  prob.y = static_cast<__half*>(Y);
+  prob.M = M;
+  prob.N = N;
+  prob.K = K;
+
+  const bool forced = path != LBL_PATH_AUTO;
+  if (!forced) {
+    path = forced_path_from_env();
+    if (path == LBL_PATH_AUTO) path = select_path(M, N, K, op, info.sm_count);
+  }
+  // The fast kernels use 16-byte vector accesses and bulk copies on every operand.
+  const bool all_aligned = aligned16(X) && aligned16(packed_w) && aligned16(scales) &&
+                           aligned16(zeros) && aligned16(Y);
+  if (!all_aligned && path != LBL_PATH_GENERIC) {
+    if (forced) return fail(LBL_ERR_UNSUPPORTED, "forced path %d needs 16-byte aligned tensors", path);
+    path = LBL_PATH_GENERIC;
+  }
+
+  cudaError_t err = cudaSuccess;
+  switch (path) {
+    case LBL_PATH_GENERIC: {
+      const bool round_weights = (flags & LBL_FLAG_ROUND_WEIGHTS) != 0 || op == 1;
+      err = lbl::launch_generic(prob, round_weights, cu_stream);
+      break;
+    }
+    case LBL_PATH_GEMV:
+    case LBL_PATH_GEMV_SPLITK: {
+      lbl::SkinnyPlan plan;
+      const int want = forced ? (path == LBL_PATH_GEMV ? 0 : 2) : -1;
+      if (!lbl::skinny_make_plan(M, N, K, want, info.sm_count, &plan)) {
+        return fail(LBL_ERR_UNSUPPORTED, "streaming kernel cannot serve M=%lld N=%lld K=%lld (needs M <= 32, K %% 256 == 0)", (long long)M, (long long)N, (long long)K);
+      }
+      float* partials = nullptr;
+      int* tickets = nullptr;
+      if (plan.nsplit > 1) {
+        const size_t need = plan.partial_bytes + plan.ticket_bytes;
+        if (workspace == nullptr || workspace_bytes < need) {
+          return fail(LBL_ERR_WORKSPACE, "split-K needs %zu bytes of scratch, got %zu", need, workspace_bytes);
+        }
+        if (!aligned16(workspace)) return fail(LBL_ERR_INVALID, "workspace must be 16-byte aligned");
+        partials = static_cast<float*>(workspace);
+        tickets = reinterpret_cast<int*>(static_cast<char*>(workspace) + plan.partial_bytes);
+      }
+      path = plan.nsplit > 1 ? LBL_PATH_GEMV_SPLITK : LBL_PATH_GEMV;
+      err = lbl::launch_skinny(prob, plan, partials, tickets, info.status_word,
+                               (flags & LBL_FLAG_PDL) != 0, cu_stream);
+      break;
+    }
+    case LBL_PATH_GEMM_TC: {
+      if (!lbl::gemm_tc_supports(M, N, K)) {
+        return fail(LBL_ERR_UNSUPPORTED, "tensor-core GEMM cannot serve M=%lld N=%lld K=%lld (needs N %% 256 == 0, K %% 256 == 0)", (long long)M, (long long)N, (long long)K);
+      }
+      err = lbl::launch_gemm_tc(prob, info.status_word, cu_stream);
+      break;
+    }
+    default:
+      return fail(LBL_ERR_INVALID, "unknown path %d", path);
+  }
+  if (err != cudaSuccess) return fail_cuda(err, "kernel launch");
+  if (path_taken != nullptr) *path_taken = path;
+  return LBL_OK;
+}
+
+int sm_count_or_default(int device_hint) {
+  int device = device_hint;
+  if (device < 0 && cudaGetDevice(&device) != cudaSuccess) return 148;
+  int sms = 0;
+  if (cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, device) != cudaSuccess || sms <= 0) {
+    cudaGetLastError();
+    return 148;  // B200
+  }
+  return sms;
+}
+
+}  // namespace
+
+extern "C" {
+
+int lbl_version(void) { return kVersion; }
+
+const char* lbl_last_error(void) { return g_error; }
+
+int lbl_w4a16_select_path(int64_t M, int64_t N, int64_t K, int op) {
+  const int forced = forced_path_from_env();
+  if (forced != LBL_PATH_AUTO) return forced;
+  return select_path(M, N, K, op, sm_count_or_default(-1));
+}
+
+size_t lbl_w4a16_workspace_bytes(int64_t M, int64_t N, int64_t K, int path) {
+  if (M <= 0 || N <= 0 || K <= 0) return 0;
+  const int sms = sm_count_or_default(-1);
+  if (path == LBL_PATH_AUTO) {
+    path = forced_path_from_env();
+    if (path == LBL_PATH_AUTO) path = select_path(M, N, K, 0, sms);
+  }
+  if (path != LBL_PATH_GEMV && path != LBL_PATH_GEMV_SPLITK) return 0;
+  lbl::SkinnyPlan plan;
+  const int want = path == LBL_PATH_GEMV_SPLITK ? 2 : -1;
+  if (!lbl::skinny_make_plan(M, N, K, want, sms, &plan)) return 0;
+  // The AUTO plan may split less than a forced split-K plan; report the larger need.
+  size_t need = plan.partial_bytes + plan.ticket_bytes;
+  lbl::SkinnyPlan auto_plan;
+  if (lbl::skinny_make_plan(M, N, K, -1, sms, &auto_plan)) {
+    const size_t other = auto_plan.partial_bytes + auto_plan.ticket_bytes;
+    if (other > need) need = other;
+  }
+  return need;
+}
+
+int lbl_w4a16_workspace_init(void* workspace, size_t workspace_bytes, int device, void* stream) {
+  if (workspace_bytes == 0) return LBL_OK;
+  if (workspace == nullptr) return fail(LBL_ERR_INVALID, "workspace is null");
+  DeviceScope scope(device);
+  if (!scope.ok()) return fail(LBL_ERR_CUDA, "cannot make device %d current", device);
+  const cudaError_t err = cudaMemsetAsync(workspace, 0, workspace_bytes, static_cast<cudaStream_t>(stream));
+  if (err != cudaSuccess) return fail_cuda(err, "cudaMemsetAsync");
+  return LBL_OK;
+}
+
+int lbl_w4a16_gemv(const void* x, const int32_t* packed_w, const float* scales,
+                   const int32_t* zeros, void* y, int64_t N, int64_t K, int group_size,
+                   void* workspace, size_t workspace_bytes, unsigned flags, int device,
+                   void* stream) {
+  if (group_size != 64 || K <= 0 || K % 64 != 0) {
+    return fail(LBL_ERR_INVALID, "Expected group_size=64 and K divisible by 64 (group_size=%d K=%lld)", group_size, (long long)K);
+  }
+  if (N <= 0 || N > 0x7fffffffLL || K > 0x7fffffffLL) return fail(LBL_ERR_INVALID, "Invalid N or K");
+  if ((reinterpret_cast<uintptr_t>(x) & 15u) != 0) return fail(LBL_ERR_INVALID, "x must be 16-byte aligned");
+  return run_linear(x, packed_w, scales, zeros, y, 1, N, K, 0, LBL_PATH_AUTO, workspace,
+                    workspace_bytes, flags, device, stream, nullptr);
+}
+
+int lbl_w4a16_gemm(const void* X, const int32_t* packed_w, const float* scales,
+                   const int32_t* zeros, void* Y, int64_t M, int64_t N, int64_t K,
+                   void* workspace, size_t workspace_bytes, unsigned flags, int device,
+                   void* stream) {
+  return run_linear(X, packed_w, scales, zeros, Y, M, N, K, 1, LBL_PATH_AUTO, workspace,
+                    workspace_bytes, flags, device, stream, nullptr);
+}
+
+int lbl_w4a16_linear(const void* X, const int32_t* packed_w, const float* scales,
+                     const int32_t* zeros, void* Y, int64_t M, int64_t N, int64_t K, int op,
+                     int path, void* workspace, size_t workspace_bytes, unsigned flags,
+                     int device, void* stream, int* path_taken) {
+  if (op != 0 && op != 1) return fail(LBL_ERR_INVALID, "op must be 0 or 1");
+  return run_linear(X, packed_w, scales, zeros, Y, M, N, K, op, path, workspace, workspace_bytes,
+                    flags, device, stream, path_taken);
+}
+
+int lbl_device_status(int device, int* status) {
+  if (status == nullptr) return fail(LBL_ERR_INVALID, "status is null");
+  DeviceScope scope(device);
+  if (!scope.ok()) return fail(LBL_ERR_CUDA, "cannot make device %d current", device);
+  DeviceInfo info;
+  const int rc = device_info(device, &info);
+  if (rc != LBL_OK) return rc;
+  cudaError_t err = cudaDeviceSynchronize();
+  if (err != cudaSuccess) return fail_cuda(err, "cudaDeviceSynchronize");
+  err = cudaMemcpy(status, info.status_word, sizeof(int), cudaMemcpyDeviceToHost);
+  if (err != cudaSuccess) return fail_cuda(err, "cudaMemcpy");
+  if (*status != 0) {
+    const int zero = 0;
+    err = cudaMemcpy(info.status_word, &zero, sizeof(int), cudaMemcpyHostToDevice);
+    if (err != cudaSuccess) return fail_cuda(err, "cudaMemcpy");
+  }
+  return LBL_OK;
+}
+
+}  // extern "C"

@@ -1,0 +1,52 @@
+// Host-side interface between the C ABI (api.cu) and the kernel translation units.
+#pragma once
+
+#include <cuda_fp16.h>
+#include <cuda_runtime.h>
+#include <stddef.h>
+#include <stdint.h>
+
+namespace lbl {
+
+// One W4A16 problem in the reference layout.  Pointers are device pointers.
+struct Problem {
+  const __half* x;         // [M, K]
+  const uint32_t* packed;  // [N, ceil(K/8)]
+  const float* scales;     // [N, ceil(K/64)]
+  const int32_t* zeros;    // [N, ceil(K/64)]
+  __half* y;               // [M, N]
+  int64_t M, N, K;
+};
+
+// ----- masked any-shape kernel (generic.cu) ----------------------------------------------------
+cudaError_t launch_generic(const Problem& p, bool round_weights_to_fp16, cudaStream_t stream);
+
+// ----- streaming skinny kernel, optional split-K (skinny.cu) -----------------------------------
+struct SkinnyPlan {
+  int kseg;         // columns of K handled by one unit; divides K; multiple of 256
+  int nsplit;       // K / kseg
+  int stage_k;      // columns of K per pipeline stage; divides kseg; multiple of 256
+  int slots;        // depth of the shared-memory ring
+  int grid;         // persistent CTAs
+  int smem_bytes;   // dynamic shared memory per CTA
+  int row_tiles;    // ceil(N / 16)
+  size_t partial_bytes;  // split-K partial sums (0 when nsplit == 1)
+  size_t ticket_bytes;   // one int per row tile (0 when nsplit == 1)
+};
+
+constexpr int kSkinnyMaxM = 32;
+
+// True when the skinny kernel can serve the shape (M <= 32, K a multiple of 256).
+bool skinny_supports(int64_t M, int64_t N, int64_t K);
+// Fills `plan` for the shape; `want_split` < 0 lets the heuristic decide, 0 forbids split-K,
+// > 0 asks for at least that many splits where the shape allows it.
+bool skinny_make_plan(int64_t M, int64_t N, int64_t K, int want_split, int sm_count,
+                      SkinnyPlan* plan);
+cudaError_t launch_skinny(const Problem& p, const SkinnyPlan& plan, float* partials, int* tickets,
+                          int* status_word, bool pdl, cudaStream_t stream);
+
+// ----- TMA + tcgen05 GEMM (gemm_tc.cu) ---------------------------------------------------------
+bool gemm_tc_supports(int64_t M, int64_t N, int64_t K);
+cudaError_t launch_gemm_tc(const Problem& p, int* status_word, cudaStream_t stream);
+
+}  // namespace lbl

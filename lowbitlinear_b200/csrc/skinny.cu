@@ -1,0 +1,511 @@
+// Streaming W4A16 kernel for skinny activations (M <= 32): the decode GEMV and its split-K form.
+//
+// The kernel is HBM-bound: 0.625 bytes per weight (packed nibble + its share of scale and zero
+// point) against 2 M flops.  Its job is to keep enough bytes in flight and to spend as few issue
+// slots per weight as possible.
+//
+// Data movement.  A persistent CTA walks a list of units; a unit is 16 weight rows by `kseg`
+// columns.  One producer warp streams the unit through a ring of shared-memory slots with 1-D
+// bulk copies (cp.async.bulk, completion counted on an mbarrier): per slot, 16 row pieces of
+// packed words plus the matching pieces of the scale and zero-point rows, each read straight
+// from the reference layout ([N, K/8] words, [N, K/64] metadata).  Row pieces land with a padded
+// pitch so that the fragment loads below are bank-conflict free.  Weight copies never depend on
+// the previous kernel in the stream, so with programmatic dependent launch they start while that
+// kernel is still draining; only the activation read waits for it.
+//
+// Arithmetic.  Eight consumer warps share a slot by quantisation group.  For one group (16 rows
+// by 64 columns) a warp loads 8 bytes per lane and row, turns each word into four half2 values
+// with one shift and four ANDs (nibbles become FP16 subnormals, see common.cuh), and issues four
+// m16n8k16 warp MMAs whose A operand is the raw levels q and whose B operand is the activation
+// block; FP32 accumulation.  The group's scale and zero point are applied once, in FP32:
+//     acc += scale * (sum_k q x  -  zero * sum_k x)
+// with the per-group activation sums computed once per CTA.  (q - zero) is never formed and the
+// scale is never rounded to FP16.
+//
+// Reduction.  The warps' partial rows are added in a fixed order through shared memory.  With
+// split-K, every unit writes FP32 partials to scratch and takes a ticket for its row tile; the
+// CTA that draws the last ticket adds the partials in split order and writes FP16, then puts the
+// ticket counter back to zero.  Results are bit-reproducible from run to run.
+#include "common.cuh"
+#include "kernels.h"
+
+#include <algorithm>
+#include <cstdlib>
+
+namespace lbl {
+namespace {
+
+constexpr int kRows = 16;
+constexpr int kConsumerWarps = 8;
+constexpr int kConsumerThreads = kConsumerWarps * 32;
+constexpr int kThreads = kConsumerThreads + 32;
+constexpr int kMaxSlots = 8;
+constexpr int kHeaderBytes = 256;
+constexpr int kMaxStageK = 2048;
+constexpr int kXfBudgetBytes = 64 * 1024;   // activation operand kept in shared memory
+constexpr int kSmemBudgetTwoCtas = 110 * 1024;
+constexpr int kSmemBudgetOneCta = 200 * 1024;
+
+struct KernelParams {
+  const __half* x;
+  const uint8_t* packed;  // byte view of the packed words
+  const uint8_t* scales;  // byte view
+  const uint8_t* zeros;   // byte view
+  __half* y;
+  float* partials;
+  int* tickets;
+  int* status;
+  int M, N, K;
+  int kseg, nsplit, stage_k, stages_per_unit, slots;
+  int row_tiles, units;
+  int packed_pitch;  // bytes between rows of a slot's packed block
+  int meta_pitch;    // bytes between rows of a slot's scale / zero block
+  int slot_bytes;
+  int sx_offset, red_offset, xf_offset, ring_offset;  // shared-memory layout
+};
+
+struct Header {
+  uint64_t full[kMaxSlots];
+  uint64_t empty[kMaxSlots];
+  int abort_flag;
+  int ticket;
+};
+static_assert(sizeof(Header) <= kHeaderBytes, "header does not fit");
+
+__device__ __forceinline__ uint32_t pack_half2(__half lo, __half hi) {
+  return static_cast<uint32_t>(__half_as_ushort(lo)) |
+         (static_cast<uint32_t>(__half_as_ushort(hi)) << 16);
+}
+
+// Builds, for the K segment starting at column `k_begin`, the MMA B operand of every
+// (group, step) and the per-group activation sums.  Runs on the 256 consumer threads.
+//
+// Column layout inside a group: lane t of a quad owns words 2t and 2t+1 (columns 16t..16t+15).
+// Word half h and nibble pair p give MMA step s = 2h + p, whose four k-slots in this lane are
+//   b0 = (x[c + 0], x[c + 4])          c = 64 G + 16 t + 8 h + 2 p
+//   b1 = (x[c + 1], x[c + 5]) / 16     (the odd nibbles carry a factor 16, see common.cuh)
+template <int NT>
+__device__ __forceinline__ void build_activation_operand(const KernelParams& p, int k_begin,
+                                                         uint2* xf, float* sx, int tid) {
+  constexpr int MC = 8 * NT;
+  const int groups = p.kseg / 64;
+  const int words_seg = p.kseg / 8;
+  for (int i = tid; i < groups * MC; i += kConsumerThreads) {
+    if (i % MC >= p.M) sx[i] = 0.0f;
+  }
+  const __half sixteenth = __float2half_rn(0.0625f);
+  const int total = p.M * words_seg;  // multiple of 32: whole warps stay together below
+  for (int idx = tid; idx < total; idx += kConsumerThreads) {
+    const int m = idx / words_seg;
+    const int wd = idx - m * words_seg;
+    const uint4 raw =
+        *reinterpret_cast<const uint4*>(p.x + static_cast<size_t>(m) * p.K + k_begin + wd * 8);
+    const __half2 v01 = *reinterpret_cast<const __half2*>(&raw.x);
+    const __half2 v23 = *reinterpret_cast<const __half2*>(&raw.y);
+    const __half2 v45 = *reinterpret_cast<const __half2*>(&raw.z);
+    const __half2 v67 = *reinterpret_cast<const __half2*>(&raw.w);
+    const __half x0 = __low2half(v01), x1 = __high2half(v01);
+    const __half x2 = __low2half(v23), x3 = __high2half(v23);
+    const __half x4 = __low2half(v45), x5 = __high2half(v45);
+    const __half x6 = __low2half(v67), x7 = __high2half(v67);
+    float sum = ((__half2float(x0) + __half2float(x1)) + (__half2float(x2) + __half2float(x3))) +
+                ((__half2float(x4) + __half2float(x5)) + (__half2float(x6) + __half2float(x7)));
+    sum += __shfl_xor_sync(0xffffffffu, sum, 1);
+    sum += __shfl_xor_sync(0xffffffffu, sum, 2);
+    sum += __shfl_xor_sync(0xffffffffu, sum, 4);
+    const int group = wd >> 3;
+    const int wq = wd & 7;
+    const int t = wq >> 1;
+    const int h = wq & 1;
+    uint2 step0, step1;
+    step0.x = pack_half2(x0, x4);
+    step0.y = pack_half2(__hmul(x1, sixteenth), __hmul(x5, sixteenth));
+    step1.x = pack_half2(x2, x6);
+    step1.y = pack_half2(__hmul(x3, sixteenth), __hmul(x7, sixteenth));
+    xf[((group * 4 + 2 * h) * p.M + m) * 4 + t] = step0;
+    xf[((group * 4 + 2 * h + 1) * p.M + m) * 4 + t] = step1;
+    if (wq == 0) sx[group * MC + m] = sum;
+  }
+}
+
+template <int NT>
+__global__ void __launch_bounds__(kThreads, (NT <= 2 ? 2 : 1)) w4a16_skinny_kernel(const KernelParams p) {
+  constexpr int MC = 8 * NT;
+  extern __shared__ __align__(128) uint8_t smem[];
+  Header* hdr = reinterpret_cast<Header*>(smem);
+  float* sx = reinterpret_cast<float*>(smem + p.sx_offset);
+  float* red = reinterpret_cast<float*>(smem + p.red_offset);
+  uint2* xf = reinterpret_cast<uint2*>(smem + p.xf_offset);
+  uint8_t* ring = smem + p.ring_offset;
+  volatile int* abort_flag = &hdr->abort_flag;
+
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < p.slots; ++s) {
+      mbar_init(&hdr->full[s], 1);
+      mbar_init(&hdr->empty[s], kConsumerWarps);
+    }
+    hdr->abort_flag = 0;
+    hdr->ticket = 0;
+    mbar_init_fence();
+  }
+  __syncthreads();
+  // The next kernel in the stream may start filling its own ring as soon as it finds room.
+  pdl_allow_next_kernel();
+
+  const int meta_bytes = p.stage_k / 16;  // bytes of one row's scales (or zeros) per stage
+  const int packed_bytes = p.stage_k / 2;
+  const int zeros_block = kRows * p.packed_pitch + kRows * p.meta_pitch;
+
+  if (warp == kConsumerWarps) {
+    // ------------------------------- producer ------------------------------------------------
+    int it = 0;
+    for (int unit = blockIdx.x; unit < p.units; unit += gridDim.x) {
+      const int ks = unit / p.row_tiles;
+      const int rt = unit - ks * p.row_tiles;
+      const int n0 = rt * kRows;
+      const int rows = min(kRows, p.N - n0);
+      for (int st = 0; st < p.stages_per_unit; ++st, ++it) {
+        const int slot = it % p.slots;
+        const int round = it / p.slots;
+        if (round > 0) {
+          mbar_wait_bounded(&hdr->empty[slot], (round - 1) & 1, abort_flag, p.status,
+                            kStatusSkinnyEmptyWait);
+        }
+        if (*abort_flag) break;
+        const int k0 = ks * p.kseg + st * p.stage_k;
+        if (lane == 0) {
+          mbar_arrive_expect_tx(&hdr->full[slot],
+                                static_cast<uint32_t>(rows * (packed_bytes + 2 * meta_bytes)));
+        }
+        __syncwarp();
+        if (lane < rows) {
+          uint8_t* base = ring + static_cast<size_t>(slot) * p.slot_bytes;
+          const size_t row = static_cast<size_t>(n0 + lane);
+          bulk_load(base + lane * p.packed_pitch, p.packed + row * (p.K / 2) + k0 / 2,
+                    packed_bytes, &hdr->full[slot]);
+          bulk_load(base + kRows * p.packed_pitch + lane * p.meta_pitch,
+                    p.scales + row * (p.K / 16) + k0 / 16, meta_bytes, &hdr->full[slot]);
+          bulk_load(base + zeros_block + lane * p.meta_pitch,
+                    p.zeros + row * (p.K / 16) + k0 / 16, meta_bytes, &hdr->full[slot]);
+        }
+      }
+      if (*abort_flag) break;
+    }
+    return;
+  }
+
+  // --------------------------------- consumers -----------------------------------------------
+  const int tid = threadIdx.x;  // 0..255
+  const int g = lane >> 2;
+  const int t = lane & 3;
+  const int groups_per_stage = p.stage_k / 64;
+  const float zero4[4] = {0.0f, 0.0f, 0.0f, 0.0f};
+
+  int it = 0;
+  int current_ks = -1;
+  for (int unit = blockIdx.x; unit < p.units; unit += gridDim.x) {
+    const int ks = unit / p.row_tiles;
+    const int rt = unit - ks * p.row_tiles;
+    const int n0 = rt * kRows;
+
+    if (ks != current_ks) {
+      // Activations are the only input the previous kernel may have produced.
+      if (current_ks < 0) pdl_wait_for_previous_kernel();
+      build_activation_operand<NT>(p, ks * p.kseg, xf, sx, tid);
+      named_barrier(1, kConsumerThreads);
+      current_ks = ks;
+    }
+
+    float acc[NT][4];
+#pragma unroll
+    for (int nt = 0; nt < NT; ++nt) {
+#pragma unroll
+      for (int i = 0; i < 4; ++i) acc[nt][i] = 0.0f;
+    }
+
+    for (int st = 0; st < p.stages_per_unit; ++st, ++it) {
+      const int slot = it % p.slots;
+      const int round = it / p.slots;
+      mbar_wait_bounded(&hdr->full[slot], round & 1, abort_flag, p.status, kStatusSkinnyFullWait);
+
+      const uint8_t* base = ring + static_cast<size_t>(slot) * p.slot_bytes;
+      const uint8_t* row_a = base + g * p.packed_pitch + t * 8;
+      const uint8_t* row_b = row_a + 8 * p.packed_pitch;
+      const float* sc_a = reinterpret_cast<const float*>(base + kRows * p.packed_pitch + g * p.meta_pitch);
+      const float* sc_b = reinterpret_cast<const float*>(base + kRows * p.packed_pitch + (g + 8) * p.meta_pitch);
+      const int* zp_a = reinterpret_cast<const int*>(base + zeros_block + g * p.meta_pitch);
+      const int* zp_b = reinterpret_cast<const int*>(base + zeros_block + (g + 8) * p.meta_pitch);
+
+      for (int G = warp; G < groups_per_stage; G += kConsumerWarps) {
+        const uint2 wa = *reinterpret_cast<const uint2*>(row_a + G * 32);
+        const uint2 wb = *reinterpret_cast<const uint2*>(row_b + G * 32);
+        const float scale_a = sc_a[G];
+        const float scale_b = sc_b[G];
+        const float zero_a = static_cast<float>(zp_a[G]);
+        const float zero_b = static_cast<float>(zp_b[G]);
+
+        uint32_t ha[8], hb[8];
+        {
+          uint32_t q[4];
+          nibbles_as_subnormal_half2(wa.x, q);
+          ha[0] = q[0]; ha[1] = q[1]; ha[2] = q[2]; ha[3] = q[3];
+          nibbles_as_subnormal_half2(wa.y, q);
+          ha[4] = q[0]; ha[5] = q[1]; ha[6] = q[2]; ha[7] = q[3];
+          nibbles_as_subnormal_half2(wb.x, q);
+          hb[0] = q[0]; hb[1] = q[1]; hb[2] = q[2]; hb[3] = q[3];
+          nibbles_as_subnormal_half2(wb.y, q);
+          hb[4] = q[0]; hb[5] = q[1]; hb[6] = q[2]; hb[7] = q[3];
+        }
+
+        const int group_in_seg = st * groups_per_stage + G;
+        const uint2* xf_group = xf + static_cast<size_t>(group_in_seg) * 4 * p.M * 4;
+        float d[NT][4];
+#pragma unroll
+        for (int s = 0; s < 4; ++s) {
+          const uint32_t a[4] = {ha[2 * s], hb[2 * s], ha[2 * s + 1], hb[2 * s + 1]};
+#pragma unroll
+          for (int nt = 0; nt < NT; ++nt) {
+            const int n = nt * 8 + g;
+            uint2 b = make_uint2(0u, 0u);
+            if (n < p.M) b = xf_group[(s * p.M + n) * 4 + t];
+            if (s == 0) {
+              mma_m16n8k16(d[nt], a, b.x, b.y, zero4);
+            } else {
+              mma_m16n8k16(d[nt], a, b.x, b.y, d[nt]);
+            }
+          }
+        }
+
+        // acc += scale * (sum q x) - (scale * zero) * (sum x); the MMA result carries the
+        // factor kNibbleUnit^-1 of the nibble encoding.
+        const float fa = scale_a * kNibbleUnit;
+        const float fb = scale_b * kNibbleUnit;
+        const float ca = -(scale_a * zero_a);
+        const float cb = -(scale_b * zero_b);
+#pragma unroll
+        for (int nt = 0; nt < NT; ++nt) {
+          const float2 sums =
+              *reinterpret_cast<const float2*>(sx + group_in_seg * MC + nt * 8 + 2 * t);
+          acc[nt][0] = fmaf(fa, d[nt][0], acc[nt][0]);
+          acc[nt][1] = fmaf(fa, d[nt][1], acc[nt][1]);
+          acc[nt][2] = fmaf(fb, d[nt][2], acc[nt][2]);
+          acc[nt][3] = fmaf(fb, d[nt][3], acc[nt][3]);
+          acc[nt][0] = fmaf(ca, sums.x, acc[nt][0]);
+          acc[nt][1] = fmaf(ca, sums.y, acc[nt][1]);
+          acc[nt][2] = fmaf(cb, sums.x, acc[nt][2]);
+          acc[nt][3] = fmaf(cb, sums.y, acc[nt][3]);
+        }
+      }
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&hdr->empty[slot]);
+    }
+
+    // ---- cross-warp reduction of the unit, fixed order ---------------------------------------
+#pragma unroll
+    for (int nt = 0; nt < NT; ++nt) {
+      float* r0 = red + (warp * kRows + g) * MC + nt * 8 + 2 * t;
+      float* r1 = red + (warp * kRows + g + 8) * MC + nt * 8 + 2 * t;
+      r0[0] = acc[nt][0];
+      r0[1] = acc[nt][1];
+      r1[0] = acc[nt][2];
+      r1[1] = acc[nt][3];
+    }
+    named_barrier(1, kConsumerThreads);
+    for (int o = tid; o < kRows * MC; o += kConsumerThreads) {
+      const int col = o / kRows;
+      const int row = o - col * kRows;
+      float v = 0.0f;
+#pragma unroll
+      for (int w = 0; w < kConsumerWarps; ++w) v += red[(w * kRows + row) * MC + col];
+      if (col < p.M && n0 + row < p.N) {
+        if (p.nsplit == 1) {
+          p.y[static_cast<size_t>(col) * p.N + n0 + row] = __float2half_rn(v);
+        } else {
+          p.partials[(static_cast<size_t>(ks) * p.M + col) * p.N + n0 + row] = v;
+        }
+      }
+    }
+    if (p.nsplit > 1) {
+      __threadfence();
+      named_barrier(1, kConsumerThreads);
+      if (tid == 0) hdr->ticket = atomicAdd(&p.tickets[rt], 1);
+      named_barrier(1, kConsumerThreads);
+      if (hdr->ticket == p.nsplit - 1) {
+        __threadfence();
+        for (int o = tid; o < kRows * MC; o += kConsumerThreads) {
+          const int col = o / kRows;
+          const int row = o - col * kRows;
+          if (col < p.M && n0 + row < p.N) {
+            float v = 0.0f;
+            for (int s = 0; s < p.nsplit; ++s) {
+              v += __ldcg(&p.partials[(static_cast<size_t>(s) * p.M + col) * p.N + n0 + row]);
+            }
+            p.y[static_cast<size_t>(col) * p.N + n0 + row] = __float2half_rn(v);
+          }
+        }
+        if (tid == 0) p.tickets[rt] = 0;
+      }
+    }
+    named_barrier(1, kConsumerThreads);
+  }
+}
+
+int env_int(const char* name, int fallback) {
+  const char* v = std::getenv(name);
+  if (v == nullptr || *v == '\0') return fallback;
+  return std::atoi(v);
+}
+
+template <int NT>
+cudaError_t launch_nt(const KernelParams& kp, const SkinnyPlan& plan, bool pdl,
+                      cudaStream_t stream) {
+  // The opt-in to large dynamic shared memory is per device and per kernel; repeating it is
+  // harmless, so a racy "done" flag is enough.
+  static bool configured[64] = {};
+  int device = 0;
+  cudaError_t err = cudaGetDevice(&device);
+  if (err != cudaSuccess) return err;
+  if (device < 0 || device >= 64 || !configured[device]) {
+    err = cudaFuncSetAttribute(w4a16_skinny_kernel<NT>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                               kSmemBudgetOneCta + 16 * 1024);
+    if (err != cudaSuccess) return err;
+    if (device >= 0 && device < 64) configured[device] = true;
+  }
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3(static_cast<unsigned>(plan.grid));
+  cfg.blockDim = dim3(kThreads);
+  cfg.dynamicSmemBytes = static_cast<size_t>(plan.smem_bytes);
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = pdl ? 1 : 0;
+  return cudaLaunchKernelEx(&cfg, w4a16_skinny_kernel<NT>, kp);
+}
+
+}  // namespace
+
+bool skinny_supports(int64_t M, int64_t N, int64_t K) {
+  return M >= 1 && M <= kSkinnyMaxM && N >= 1 && K >= 256 && K % 256 == 0 &&
+         N <= 0x7fffffffLL - kRows && K <= (1 << 24) && M * N <= 0x7fffffffLL;
+}
+
+bool skinny_make_plan(int64_t M, int64_t N, int64_t K, int want_split, int sm_count,
+                      SkinnyPlan* plan) {
+  if (!skinny_supports(M, N, K)) return false;
+  const int m = static_cast<int>(M);
+  const int k = static_cast<int>(K);
+  const int nt = m <= 8 ? 1 : (m <= 16 ? 2 : 4);
+  const int mc = 8 * nt;
+  const int row_tiles = static_cast<int>((N + kRows - 1) / kRows);
+  const int chunks = k / 256;
+
+  // Candidate splits: every divisor d of K / 256 gives kseg = K / d.
+  const int kseg_cap = std::max(256, (kXfBudgetBytes / (2 * m)) / 256 * 256);
+  const int target_units = 2 * sm_count;
+  int forced = env_int("LBL_SKINNY_NSPLIT", 0);
+  if (want_split > 0) forced = want_split;
+  int nsplit = 0;
+  for (int d = 1; d <= chunks; ++d) {
+    if (chunks % d != 0) continue;
+    const int kseg = k / d;
+    if (kseg > kseg_cap) continue;
+    nsplit = d;
+    if (forced > 0) {
+      if (d >= forced) break;
+      continue;
+    }
+    if (want_split == 0) break;                                      // no more than necessary
+    if (static_cast<int64_t>(row_tiles) * d >= target_units) break;  // enough units
+    if (kseg <= 1024) break;                                         // pieces would get too small
+  }
+  if (nsplit == 0) return false;
+  const int kseg = k / nsplit;
+
+  int stage_k = 256;
+  const int stage_cap = std::min(kMaxStageK, std::max(256, env_int("LBL_SKINNY_STAGE_K", kMaxStageK)));
+  for (int c = stage_cap / 256; c >= 1; --c) {
+    if (kseg % (256 * c) == 0) {
+      stage_k = 256 * c;
+      break;
+    }
+  }
+
+  const int packed_pitch = stage_k / 2 + 32;
+  const int meta_pitch = stage_k / 16 + 16;
+  const int slot_bytes = kRows * packed_pitch + 2 * kRows * meta_pitch;
+  const int sx_bytes = (kseg / 64) * mc * 4;
+  const int red_bytes = kConsumerWarps * kRows * mc * 4;
+  const int xf_bytes = m * kseg * 2;
+  const int fixed = kHeaderBytes + sx_bytes + red_bytes + xf_bytes;
+
+  const int ctas_per_sm = std::max(1, std::min(2, env_int("LBL_SKINNY_CTAS_PER_SM", 2)));
+  int budget = ctas_per_sm == 2 ? kSmemBudgetTwoCtas : kSmemBudgetOneCta;
+  int per_sm = ctas_per_sm;
+  if (fixed + 2 * slot_bytes > budget) {
+    budget = kSmemBudgetOneCta;
+    per_sm = 1;
+  }
+  int slots = (budget - fixed) / slot_bytes;
+  slots = std::min(slots, std::min(kMaxSlots, std::max(2, env_int("LBL_SKINNY_SLOTS", kMaxSlots))));
+  if (slots < 2) return false;
+
+  const int64_t units = static_cast<int64_t>(row_tiles) * nsplit;
+  plan->kseg = kseg;
+  plan->nsplit = nsplit;
+  plan->stage_k = stage_k;
+  plan->slots = slots;
+  plan->grid = static_cast<int>(std::min<int64_t>(units, static_cast<int64_t>(per_sm) * sm_count));
+  plan->smem_bytes = fixed + slots * slot_bytes;
+  plan->row_tiles = row_tiles;
+  plan->partial_bytes = nsplit > 1 ? static_cast<size_t>(nsplit) * M * N * sizeof(float) : 0;
+  plan->ticket_bytes = nsplit > 1 ? static_cast<size_t>(row_tiles) * sizeof(int) : 0;
+  return units <= 0x7fffffffLL;
+}
+
+cudaError_t launch_skinny(const Problem& p, const SkinnyPlan& plan, float* partials, int* tickets,
+                          int* status_word, bool pdl, cudaStream_t stream) {
+  const int m = static_cast<int>(p.M);
+  const int nt = m <= 8 ? 1 : (m <= 16 ? 2 : 4);
+  const int mc = 8 * nt;
+  KernelParams kp;
+  kp.x = p.x;
+  kp.packed = reinterpret_cast<const uint8_t*>(p.packed);
+  kp.scales = reinterpret_cast<const uint8_t*>(p.scales);
+  kp.zeros = reinterpret_cast<const uint8_t*>(p.zeros);
+  kp.y = p.y;
+  kp.partials = partials;
+  kp.tickets = tickets;
+  kp.status = status_word;
+  kp.M = m;
+  kp.N = static_cast<int>(p.N);
+  kp.K = static_cast<int>(p.K);
+  kp.kseg = plan.kseg;
+  kp.nsplit = plan.nsplit;
+  kp.stage_k = plan.stage_k;
+  kp.stages_per_unit = plan.kseg / plan.stage_k;
+  kp.slots = plan.slots;
+  kp.row_tiles = plan.row_tiles;
+  kp.units = plan.row_tiles * plan.nsplit;
+  kp.packed_pitch = plan.stage_k / 2 + 32;
+  kp.meta_pitch = plan.stage_k / 16 + 16;
+  kp.slot_bytes = kRows * kp.packed_pitch + 2 * kRows * kp.meta_pitch;
+  kp.sx_offset = kHeaderBytes;
+  kp.red_offset = kp.sx_offset + (plan.kseg / 64) * mc * 4;
+  kp.xf_offset = kp.red_offset + kConsumerWarps * kRows * mc * 4;
+  kp.ring_offset = kp.xf_offset + m * plan.kseg * 2;
+  switch (nt) {
+    case 1:
+      return launch_nt<1>(kp, plan, pdl, stream);
+    case 2:
+      return launch_nt<2>(kp, plan, pdl, stream);
+    default:
+      return launch_nt<4>(kp, plan, pdl, stream);
+  }
+}
+
+}  // namespace lbl

@@ -1,0 +1,222 @@
+"""The drop-in boundary: the native library loads, exports every entry point the header
+declares, registers the reference's two operator schemas, and a missing library is an error
+for CUDA work but not for CPU work.  No GPU compute happens in the CPU-marked tests."""
+import ctypes
+import os
+import re
+import shutil
+import subprocess
+import sys
+from pathlib import Path
+
+import pytest
+import torch
+
+ROOT = Path(__file__).resolve().parents[1]
+HEADER = ROOT / "include" / "lowbitlinear_b200.h"
+LIBRARY = ROOT / "lowbitlinear_b200" / "_C.so"
+
+needs_library = pytest.mark.skipif(not LIBRARY.is_file(), reason="native library not built (python -m lowbitlinear_b200.build)")
+
+
+def declared_entry_points():
+    text = re.sub(r"/\*.*?\*/", "", HEADER.read_text(), flags=re.S)
+    return sorted(set(re.findall(r"\b(lbl_\w+)\s*\(", text)))
+
+
+def test_header_declares_the_boundary():
+    names = declared_entry_points()
+    for required in ("lbl_w4a16_gemv", "lbl_w4a16_gemm", "lbl_w4a16_linear", "lbl_w4a16_workspace_bytes",
+                     "lbl_w4a16_workspace_init", "lbl_w4a16_select_path", "lbl_last_error", "lbl_version",
+                     "lbl_device_status"):
+        assert required in names
+
+
+@needs_library
+def test_library_exports_every_declared_symbol():
+    lib = ctypes.CDLL(str(LIBRARY))
+    for name in declared_entry_points():
+        assert hasattr(lib, name), f"{name} is declared in the header but not exported"
+    lib.lbl_version.restype = ctypes.c_int
+    assert lib.lbl_version() >= 100
+    lib.lbl_last_error.restype = ctypes.c_char_p
+    assert lib.lbl_last_error() == b""
+
+
+@needs_library
+def test_argument_errors_need_no_gpu():
+    """Checks that run before any CUDA call: codes and messages of the C ABI."""
+    lib = ctypes.CDLL(str(LIBRARY))
+    lib.lbl_last_error.restype = ctypes.c_char_p
+    p, i64, i32, u32, sz = ctypes.c_void_p, ctypes.c_int64, ctypes.c_int, ctypes.c_uint, ctypes.c_size_t
+    lib.lbl_w4a16_gemv.argtypes = [p, p, p, p, p, i64, i64, i32, p, sz, u32, i32, p]
+    rc = lib.lbl_w4a16_gemv(None, None, None, None, None, 128, 65, 64, None, 0, 0, 0, None)
+    assert rc == -1 and b"divisible by 64" in lib.lbl_last_error()
+    rc = lib.lbl_w4a16_gemv(None, None, None, None, None, 128, 64, 32, None, 0, 0, 0, None)
+    assert rc == -1 and b"group_size=64" in lib.lbl_last_error()
+    rc = lib.lbl_w4a16_gemv(None, None, None, None, None, 0, 64, 64, None, 0, 0, 0, None)
+    assert rc == -1 and b"Invalid N or K" in lib.lbl_last_error()
+    rc = lib.lbl_w4a16_gemv(8, None, None, None, None, 128, 64, 64, None, 0, 0, 0, None)
+    assert rc == -1 and b"16-byte aligned" in lib.lbl_last_error()
+    lib.lbl_w4a16_gemm.argtypes = [p, p, p, p, p, i64, i64, i64, p, sz, u32, i32, p]
+    assert lib.lbl_w4a16_gemm(None, None, None, None, None, 0, 32, 65, None, 0, 0, 0, None) == 0  # empty output
+    assert lib.lbl_w4a16_gemm(None, None, None, None, None, -1, 32, 65, None, 0, 0, 0, None) == -1
+
+
+@needs_library
+def test_dispatcher_choices_and_scratch_sizes():
+    from lowbitlinear_b200 import _ops
+    from lowbitlinear_b200._extension import load_cuda_extension
+
+    assert load_cuda_extension(required=True)
+    env_backup = {k: os.environ.pop(k, None) for k in ("LBL_FORCE_PATH", "LBL_SKINNY_NSPLIT", "LBL_TC_MIN_M")}
+    try:
+        name = lambda m, n, k: _ops.PATH_NAMES[_ops.select_path(m, n, k)]
+        # Decode shapes stream; a small N or a long K is split across CTAs.
+        assert name(1, 6144, 4096) == "gemv"
+        assert name(1, 24576, 4096) == "gemv"
+        assert name(1, 4096, 4096) == "gemv_splitk"
+        assert name(1, 4096, 12288) == "gemv_splitk"
+        assert name(8, 4096, 12288) == "gemv_splitk"   # activations of one segment must fit on chip
+        # Prefill shapes go to the tensor cores; ragged shapes to the masked kernel.
+        assert name(2048, 24576, 4096) == "gemm_tc"
+        assert name(128, 4096, 12288) == "gemm_tc"
+        assert name(5, 9, 70) == "generic"
+        assert name(1, 129, 64) == "generic"
+        assert name(2048, 129, 4096) == "generic"
+        ws = _ops._lib.lbl_w4a16_workspace_bytes
+        assert ws(1, 6144, 4096, _ops.PATH_AUTO) == 0
+        # nsplit * M * N floats + one counter per 16-row tile
+        assert ws(1, 4096, 4096, _ops.PATH_AUTO) == 2 * 4096 * 4 + 256 * 4
+        assert ws(2048, 24576, 4096, _ops.PATH_AUTO) == 0
+    finally:
+        for k, v in env_backup.items():
+            if v is not None:
+                os.environ[k] = v
+
+
+@needs_library
+def test_autoload_registers_reference_schemas_once():
+    """Fresh process: no JIT, one load_library call over three loads, exact schema strings,
+    CUDA kernels registered (the contract of the reference's tests/test_api_dispatch.py:62-92)."""
+    code = """
+import torch
+import torch.utils.cpp_extension as cpp
+def forbidden(*args, **kwargs):
+    raise AssertionError('JIT compilation is forbidden')
+cpp.load = forbidden
+cpp.load_inline = forbidden
+calls = []
+original = torch.ops.load_library
+def record(path):
+    calls.append(path)
+    return original(path)
+torch.ops.load_library = record
+import lowbitlinear_b200
+from lowbitlinear_b200._extension import load_cuda_extension
+for _ in range(3):
+    assert load_cuda_extension(required=True)
+assert len(calls) == 1, calls
+assert str(torch.ops.lowbitlinear_ext.w4a16_gemv_warp_vec.default._schema) == 'lowbitlinear_ext::w4a16_gemv_warp_vec(Tensor x, Tensor packed_w, Tensor scales, Tensor zeros, int group_size) -> Tensor'
+assert str(torch.ops.lowbitlinear_cute_w4a16.gemm.default._schema) == 'lowbitlinear_cute_w4a16::gemm(Tensor X, Tensor packed_w, Tensor scales, Tensor zeros) -> Tensor'
+for name in ('lowbitlinear_ext::w4a16_gemv_warp_vec', 'lowbitlinear_cute_w4a16::gemm'):
+    assert torch._C._dispatch_has_kernel_for_dispatch_key(name, 'CUDA'), name
+    assert not torch._C._dispatch_has_kernel_for_dispatch_key(name, 'CPU'), name
+if torch.cuda.is_available():
+    for m, n, k in ((1, 128, 64), (5, 9, 70), (1, 256, 512)):
+        layer = lowbitlinear_b200.QuantizedLinear.from_float(torch.ones(n, k, device='cuda'))
+        actual = layer(torch.ones(m, k, dtype=torch.float16, device='cuda'))
+        assert torch.equal(actual, torch.full_like(actual, float(k)))
+    torch.cuda.synchronize()
+"""
+    subprocess.run([sys.executable, "-c", code], check=True, timeout=180, cwd=ROOT)
+
+
+@needs_library
+def test_cpu_tensors_are_rejected_by_the_operators():
+    from lowbitlinear_b200._extension import load_cuda_extension
+
+    assert load_cuda_extension(required=True)
+    args = (torch.ones(1, 64, dtype=torch.float16), torch.zeros(128, 8, dtype=torch.int32),
+            torch.ones(128, 1), torch.zeros(128, 1, dtype=torch.int32))
+    with pytest.raises(NotImplementedError, match="CPU"):
+        torch.ops.lowbitlinear_ext.w4a16_gemv_warp_vec(*args, 64)
+    with pytest.raises(NotImplementedError, match="CPU"):
+        torch.ops.lowbitlinear_cute_w4a16.gemm(*args)
+
+
+@pytest.fixture
+def python_only_package(tmp_path):
+    package = tmp_path / "lowbitlinear_b200"
+    package.mkdir()
+    for path in (ROOT / "lowbitlinear_b200").glob("*.py"):
+        shutil.copy2(path, package / path.name)
+    return tmp_path
+
+
+def test_cpu_api_works_without_the_native_library(python_only_package):
+    tmp_path = python_only_package
+    code = """
+from pathlib import Path
+import pytest
+import torch
+import lowbitlinear_b200
+from lowbitlinear_b200 import QuantizedLinear
+from lowbitlinear_b200._extension import load_cuda_extension
+assert Path(lowbitlinear_b200.__file__).resolve().parent == Path.cwd() / 'lowbitlinear_b200'
+assert not load_cuda_extension()
+layer = QuantizedLinear.from_float(torch.ones(3, 65))
+assert torch.equal(layer(torch.ones(2, 65, dtype=torch.float16)), torch.full((2, 3), 65., dtype=torch.float16))
+with pytest.raises(ImportError, match='--no-build-isolation'):
+    load_cuda_extension(required=True)
+"""
+    env = dict(os.environ, CUDA_VISIBLE_DEVICES="", PYTHONPATH=str(tmp_path))
+    subprocess.run([sys.executable, "-c", code], cwd=tmp_path, env=env, check=True, timeout=180)
+
+
+@pytest.mark.gpu
+def test_cuda_forward_without_the_native_library_is_an_error(python_only_package, cuda_device):
+    """A missing build must never turn into a silent fallback."""
+    tmp_path = python_only_package
+    code = """
+import pytest
+import torch
+from lowbitlinear_b200 import QuantizedLinear
+layer = QuantizedLinear.from_float(torch.ones(128, 64, device='cuda'))
+with pytest.raises(ImportError, match='python -m lowbitlinear_b200.build'):
+    layer(torch.ones(1, 64, device='cuda', dtype=torch.float16))
+with pytest.raises(ImportError):
+    layer(torch.ones(4, 64, device='cuda', dtype=torch.float16))
+"""
+    env = dict(os.environ, PYTHONPATH=str(tmp_path))
+    subprocess.run([sys.executable, "-c", code], cwd=tmp_path, env=env, check=True, timeout=180)
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("op_name", ["gemv", "gemm"])
+def test_operator_on_noncurrent_gpu(op_name, cuda_ops):
+    if torch.cuda.device_count() < 2:
+        pytest.skip("needs two GPUs")
+    code = """
+import sys
+import torch
+import lowbitlinear_b200
+from lowbitlinear_b200.quantization import pack_int4
+with torch.cuda.device(1):
+    x = torch.ones(1, 256, device='cuda:1', dtype=torch.float16)
+    packed = pack_int4(torch.ones(128, 256, device='cuda:1', dtype=torch.uint8))
+    scales = torch.ones(128, 4, device='cuda:1')
+    zeros = torch.zeros(128, 4, device='cuda:1', dtype=torch.int32)
+    torch.cuda.synchronize(1)
+torch.cuda.set_device(0)
+if sys.argv[1] == 'gemv':
+    actual = torch.ops.lowbitlinear_ext.w4a16_gemv_warp_vec(x, packed, scales, zeros, 64)
+else:
+    actual = torch.ops.lowbitlinear_cute_w4a16.gemm(x, packed, scales, zeros)
+torch.cuda.synchronize(0)
+torch.cuda.synchronize(1)
+assert torch.cuda.current_device() == 0
+assert actual.device == x.device
+assert torch.equal(actual, torch.full_like(actual, 256.))
+"""
+    subprocess.run([sys.executable, "-c", code, op_name], check=True, timeout=180, cwd=ROOT)
