@@ -1,0 +1,108 @@
+"""Sharding a quantised linear across GPUs: N-split (column parallel) and K-split (row parallel).
+
+The reference has no multi-GPU code; these helpers sit on top of ``QuantizedLinear`` and do
+not change it.  Quantisation is independent per (row, 64-column group), so cutting the packed
+tensors gives exactly the bits that quantising the cut weight would give:
+
+* column parallel -- rank r keeps rows ``[r N / g, (r + 1) N / g)`` of packed words, scales and
+  zero points (contiguous row slices); the activation is replicated; outputs are the rank's
+  column block of Y, optionally all-gathered along N.  No communication on the data path.
+* row parallel    -- rank r keeps columns ``[r K / g, (r + 1) K / g)`` (a multiple of 64, so whole
+  groups and whole packed words), made contiguous once; it multiplies its slice of the
+  activation and the partial outputs are summed with an all-reduce.
+
+One process per GPU; ``torch.distributed`` (NCCL on GPUs, gloo on CPU) carries the collectives.
+"""
+import torch
+import torch.distributed as dist
+
+from .linear import QuantizedLinear
+
+
+def _world(group):
+    return dist.get_rank(group), dist.get_world_size(group)
+
+
+def shard_column_parallel(layer, rank, world_size):
+    """Rows ``[rank N / g, (rank + 1) N / g)`` of ``layer`` as a new ``QuantizedLinear``."""
+    n = layer.out_features
+    if n % world_size != 0:
+        raise ValueError(f"out_features {n} is not divisible by {world_size} ranks")
+    rows = slice(rank * n // world_size, (rank + 1) * n // world_size)
+    return QuantizedLinear(
+        layer.packed_weight[rows].contiguous(), layer.scales[rows].contiguous(),
+        layer.zeros[rows].contiguous(), layer.group_size, in_features=layer.in_features)
+
+
+def shard_row_parallel(layer, rank, world_size):
+    """Columns ``[rank K / g, (rank + 1) K / g)`` of ``layer`` as a new ``QuantizedLinear``.
+
+    The cut must fall on a group boundary that is also a packed-word boundary."""
+    k, gs = layer.in_features, layer.group_size
+    if k % world_size != 0:
+        raise ValueError(f"in_features {k} is not divisible by {world_size} ranks")
+    part = k // world_size
+    if part % gs != 0 or part % 8 != 0:
+        raise ValueError(f"K / ranks = {part} must be a multiple of group_size {gs} and of 8")
+    words = slice(rank * part // 8, (rank + 1) * part // 8)
+    groups = slice(rank * part // gs, (rank + 1) * part // gs)
+    return QuantizedLinear(
+        layer.packed_weight[:, words].contiguous(), layer.scales[:, groups].contiguous(),
+        layer.zeros[:, groups].contiguous(), gs, in_features=part)
+
+
+class ColumnParallelLinear(torch.nn.Module):
+    """N-split linear.  ``forward(x)`` takes the full activation ``[M, K]`` and returns this
+    rank's ``[M, N / g]`` block, or the full ``[M, N]`` after an all-gather when
+    ``gather_output`` is set."""
+
+    def __init__(self, shard, group=None, gather_output=False):
+        super().__init__()
+        self.shard = shard
+        self.group = group
+        self.gather_output = gather_output
+
+    @classmethod
+    def from_full(cls, layer, group=None, gather_output=False):
+        rank, world = _world(group)
+        return cls(shard_column_parallel(layer, rank, world), group, gather_output)
+
+    def forward(self, x):
+        y = self.shard(x)
+        if not self.gather_output:
+            return y
+        _, world = _world(self.group)
+        if world == 1:
+            return y
+        # Ranks own column blocks: gather into [g, M, N/g] and interleave the blocks per row.
+        m, n_local = y.shape
+        gathered = torch.empty((world * m, n_local), dtype=y.dtype, device=y.device)
+        dist.all_gather_into_tensor(gathered, y.contiguous(), group=self.group)
+        return gathered.view(world, m, n_local).permute(1, 0, 2).reshape(m, world * n_local)
+
+
+class RowParallelLinear(torch.nn.Module):
+    """K-split linear.  ``forward(x_local)`` takes this rank's ``[M, K / g]`` slice of the
+    activation (or the full ``[M, K]`` with ``input_is_parallel=False``) and returns the
+    all-reduced ``[M, N]``."""
+
+    def __init__(self, shard, group=None, input_is_parallel=True):
+        super().__init__()
+        self.shard = shard
+        self.group = group
+        self.input_is_parallel = input_is_parallel
+
+    @classmethod
+    def from_full(cls, layer, group=None, input_is_parallel=True):
+        rank, world = _world(group)
+        return cls(shard_row_parallel(layer, rank, world), group, input_is_parallel)
+
+    def forward(self, x):
+        rank, world = _world(self.group)
+        if not self.input_is_parallel:
+            part = self.shard.in_features
+            x = x[:, rank * part:(rank + 1) * part].contiguous()
+        y = self.shard(x)
+        if world > 1:
+            dist.all_reduce(y, op=dist.ReduceOp.SUM, group=self.group)
+        return y

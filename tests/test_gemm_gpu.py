@@ -1,0 +1,199 @@
+"""Any-shape operator on the GPU, through the C ABI: masked tails, empty dimensions, exactness
+and operand-policy cases, the tensor-core path at prefill sizes, error contract, streams.
+Mirrors the intent of the reference's tests/test_cute_w4a16_gemm.py."""
+import pytest
+import torch
+
+from conftest import ATOL, RTOL, assert_north_star_parity, oracle_linear, seeded_layer, torch_fp32_linear
+from lowbitlinear_b200.quantization import pack_int4, quantize_int4
+
+pytestmark = pytest.mark.gpu
+
+SHAPES = [
+    (1, 1, 1), (4, 9, 7), (4, 8, 8), (4, 8, 63), (32, 32, 64), (17, 23, 65), (5, 9, 70),
+    (6, 10, 71), (31, 33, 127), (6, 10, 128), (33, 37, 129), (64, 65, 130), (79, 70, 192),
+    (32, 64, 512), (7, 35, 4096),
+    # both sides of 64-wide tile boundaries, with K tails
+    (63, 63, 63), (65, 63, 64), (63, 65, 65), (65, 65, 129), (127, 129, 192),
+    # shapes the streaming kernel serves under this operator (K % 256 == 0, M <= 32)
+    (2, 100, 256), (8, 129, 512), (16, 257, 1024), (31, 48, 768),
+]
+
+
+@pytest.mark.parametrize("m,n,k", SHAPES)
+@pytest.mark.parametrize("real_quant", [False, True], ids=["synthetic-int4", "real-quantization"])
+def test_gemm_against_oracle(m, n, k, real_quant, cuda_ops):
+    x = torch.randn(m, k, device=cuda_ops, dtype=torch.float16)
+    if real_quant:
+        q, scales, zeros = quantize_int4(torch.randn(n, k, device=cuda_ops, dtype=torch.float16))
+    else:
+        q = torch.randint(0, 16, (n, k), device=cuda_ops, dtype=torch.uint8)
+        q[:, 7::8] = 15  # top nibble set: negative packed words
+        groups = (k + 63) // 64
+        scales = torch.rand(n, groups, device=cuda_ops) * .08 + .01
+        zeros = torch.randint(0, 16, (n, groups), device=cuda_ops, dtype=torch.int32)
+    args = x, pack_int4(q), scales, zeros
+    actual = torch.ops.lowbitlinear_cute_w4a16.gemm(*args)
+    assert actual.shape == (m, n) and actual.dtype == torch.float16
+    assert actual.device == x.device and torch.isfinite(actual).all()
+    torch.testing.assert_close(actual.cpu(), oracle_linear(*args, mma=True), atol=ATOL, rtol=RTOL)
+
+
+@pytest.mark.parametrize("m,n,k", [(32, 32, 64), (17, 23, 129), (65, 65, 129), (4, 64, 512), (130, 256, 512)])
+def test_exact_multistage_accumulation(m, n, k, cuda_ops):
+    x = torch.ones(m, k, device=cuda_ops, dtype=torch.float16)
+    packed = pack_int4(torch.full((n, k), 5, device=cuda_ops, dtype=torch.uint8))
+    scales = torch.full((n, (k + 63) // 64), .25, device=cuda_ops)
+    zeros = torch.full_like(scales, 3, dtype=torch.int32)
+    actual = torch.ops.lowbitlinear_cute_w4a16.gemm(x, packed, scales, zeros)
+    torch.testing.assert_close(actual, torch.full_like(actual, k * .5), rtol=0, atol=0)
+
+
+@pytest.mark.parametrize("m,n,k", [(33, 65, 129), (65, 129, 129), (5, 64, 256), (200, 256, 256)])
+def test_one_hot_mapping(m, n, k, cuda_ops):
+    """Each weight row selects one column of X: checks the (row, column) mapping of every path,
+    including the swizzled shared-memory tiles of the tensor-core kernel."""
+    x = (torch.arange(m * k, device=cuda_ops).reshape(m, k) % 101).half()
+    q = torch.zeros(n, k, dtype=torch.uint8, device=cuda_ops)
+    positions = (torch.arange(n, device=cuda_ops) * 2) % k
+    q[torch.arange(n, device=cuda_ops), positions] = 1
+    scales = torch.ones(n, (k + 63) // 64, device=cuda_ops)
+    zeros = torch.zeros_like(scales, dtype=torch.int32)
+    actual = torch.ops.lowbitlinear_cute_w4a16.gemm(x, pack_int4(q), scales, zeros)
+    torch.testing.assert_close(actual, x[:, positions], rtol=0, atol=0)
+
+
+def test_fp16_operand_policy_of_the_masked_kernel(cuda_ops):
+    """Scales 1.0004 and 1.03 tell FP16-rounded weights from FP32 weights."""
+    x = torch.ones(1, 65, device=cuda_ops, dtype=torch.float16)
+    q = torch.ones(1, 65, device=cuda_ops, dtype=torch.uint8)
+    scales = torch.tensor([[1.0004, 1.03]], device=cuda_ops)
+    zeros = torch.zeros(1, 2, device=cuda_ops, dtype=torch.int32)
+    args = x, pack_int4(q), scales, zeros
+    expected = oracle_linear(*args, mma=True)
+    assert not torch.equal(expected, oracle_linear(*args))
+    torch.testing.assert_close(torch.ops.lowbitlinear_cute_w4a16.gemm(*args).cpu(), expected, rtol=0, atol=0)
+
+
+def test_fp16_operand_policy_of_the_tensor_core_kernel(cuda_ops):
+    """Same distinction at a shape the tcgen05 kernel serves: every product is exact, so the
+    result must equal the FP16-rounded-weight oracle bit for bit."""
+    from lowbitlinear_b200 import _ops
+
+    m, n, k = 130, 256, 256
+    x = torch.zeros(m, k, device=cuda_ops, dtype=torch.float16)
+    x[torch.arange(m), torch.arange(m) % k] = 1.0  # one-hot rows pick single weights
+    q = torch.randint(0, 16, (n, k), device=cuda_ops, dtype=torch.uint8)
+    scales = torch.rand(n, k // 64, device=cuda_ops) * 0.1 + 1.0
+    zeros = torch.randint(0, 16, (n, k // 64), device=cuda_ops, dtype=torch.int32)
+    args = x, pack_int4(q), scales, zeros
+    y, taken = _ops.linear_forced(*args, _ops.PATH_GEMM_TC)
+    assert taken == _ops.PATH_GEMM_TC
+    assert torch.equal(y.cpu(), oracle_linear(*args, mma=True))
+
+
+@pytest.mark.parametrize("m,n,k", [(1, 256, 256), (127, 256, 512), (128, 512, 256), (129, 256, 1024),
+                                   (256, 256, 2048), (257, 768, 768), (300, 512, 4096), (513, 256, 1536)])
+def test_tensor_core_path_against_oracle(m, n, k, cuda_ops):
+    from lowbitlinear_b200 import _ops
+
+    x, packed, scales, zeros = seeded_layer(m, n, k, seed=m + n + k, std=1.0, device=cuda_ops)
+    y, taken = _ops.linear_forced(x, packed, scales, zeros, _ops.PATH_GEMM_TC)
+    assert taken == _ops.PATH_GEMM_TC
+    torch.testing.assert_close(y.cpu(), oracle_linear(x, packed, scales, zeros, mma=True), atol=ATOL, rtol=RTOL)
+
+
+@pytest.mark.parametrize("name,n,k,seed", [("gate_up", 24576, 4096, 2), ("down", 4096, 12288, 3)])
+@pytest.mark.parametrize("m", [128, 2048])
+def test_prefill_shapes_meet_the_benchmark_tolerance(name, n, k, seed, m, cuda_ops):
+    """Benchmark config 4 at full size, checked against an FP32 evaluation on the GPU
+    (TF32 off) and, on a slice of rows, against the numpy oracle."""
+    from lowbitlinear_b200 import QuantizedLinear, _ops
+
+    x, packed, scales, zeros = seeded_layer(m, n, k, seed=seed, device=cuda_ops)
+    assert _ops.select_path(m, n, k) == _ops.PATH_GEMM_TC
+    layer = QuantizedLinear(packed, scales, zeros, in_features=k)
+    y = layer(x)
+    assert_north_star_parity(y, torch_fp32_linear(x, packed, scales, zeros))
+    rows = slice(0, 512)
+    assert_north_star_parity(y[:8, rows], oracle_linear(x[:8], packed[rows], scales[rows], zeros[rows]))
+    # Size-independent properties: doubling X doubles Y exactly (powers of two commute with
+    # every rounding in this kernel), and a zero X gives a zero Y.
+    assert torch.equal(layer(x * 2), y * 2)
+    assert torch.count_nonzero(layer(torch.zeros_like(x))) == 0
+
+
+@pytest.mark.parametrize("m,n,k", [(32, 32, 0), (0, 32, 65), (32, 0, 65), (0, 0, 0)])
+def test_empty_dimensions(m, n, k, cuda_ops):
+    x = torch.empty(m, k, device=cuda_ops, dtype=torch.float16)
+    packed = torch.empty(n, (k + 7) // 8, device=cuda_ops, dtype=torch.int32)
+    scales = torch.empty(n, (k + 63) // 64, device=cuda_ops)
+    zeros = torch.empty_like(scales, dtype=torch.int32)
+    actual = torch.ops.lowbitlinear_cute_w4a16.gemm(x, packed, scales, zeros)
+    assert actual.shape == (m, n) and actual.dtype == x.dtype and actual.device == x.device
+    assert torch.count_nonzero(actual) == 0
+
+
+@pytest.fixture
+def small_inputs(cuda_ops):
+    def make(n=129, k=256, seed=42):
+        g = torch.Generator(device=cuda_ops).manual_seed(seed)
+        x = torch.randn(1, k, device=cuda_ops, dtype=torch.float16, generator=g)
+        w = torch.randn(n, k, device=cuda_ops, dtype=torch.float16, generator=g)
+        q, scales, zeros = quantize_int4(w)
+        return x, pack_int4(q), scales, zeros
+    return make
+
+
+@pytest.mark.parametrize("index", range(4), ids=["x", "packed", "scales", "zeros"])
+@pytest.mark.parametrize("bad", ["dtype", "rank", "noncontiguous", "cpu"])
+def test_invalid_tensor_contract(index, bad, small_inputs):
+    args = list(small_inputs())
+    tensor = args[index]
+    if bad == "dtype":
+        args[index] = tensor.double()
+        match = ["float16", "int32", "float32", "int32"][index]
+    elif bad == "rank":
+        args[index] = tensor.flatten()
+        match = "2D"
+    elif bad == "noncontiguous":
+        args[index] = torch.zeros(tensor.shape[0], tensor.shape[1] * 2, device=tensor.device, dtype=tensor.dtype)[:, ::2]
+        assert not args[index].is_contiguous()
+        match = "contiguous"
+    else:
+        args[index] = tensor.cpu()
+        match = "CUDA"
+    with pytest.raises(RuntimeError, match=match):
+        torch.ops.lowbitlinear_cute_w4a16.gemm(*args)
+
+
+@pytest.mark.parametrize("index,match", [(1, "packed_w must have shape"), (2, "scales must have shape"), (3, "zeros must have shape")])
+def test_invalid_metadata_shape(index, match, small_inputs):
+    args = list(small_inputs())
+    args[index] = args[index][:, :-1].contiguous()
+    with pytest.raises(RuntimeError, match=match):
+        torch.ops.lowbitlinear_cute_w4a16.gemm(*args)
+
+
+@pytest.mark.parametrize("m,n,k", [(1, 37, 256), (200, 256, 512)])
+def test_uses_current_stream(m, n, k, cuda_ops):
+    x, packed, scales, zeros = seeded_layer(m, n, k, seed=5, std=1.0, device=cuda_ops)
+    stream = torch.cuda.Stream()
+    stream.wait_stream(torch.cuda.current_stream())
+    with torch.cuda.stream(stream):
+        x2 = x * 2
+        actual = torch.ops.lowbitlinear_cute_w4a16.gemm(x2, packed, scales, zeros)
+        consumed = actual + 1
+    torch.cuda.current_stream().wait_stream(stream)
+    expected = oracle_linear(x2, packed, scales, zeros, mma=True) + 1
+    torch.testing.assert_close(consumed.cpu(), expected, atol=ATOL, rtol=RTOL)
+
+
+def test_misaligned_views_fall_back_to_the_masked_kernel(cuda_ops):
+    """Vector loads need 16-byte alignment; an offset view must still give the right answer."""
+    x, packed, scales, zeros = seeded_layer(4, 64, 512, seed=9, std=1.0, device=cuda_ops)
+    storage = torch.empty(x.numel() + 1, device=x.device, dtype=x.dtype)
+    shifted = storage[1:].view_as(x).copy_(x)
+    assert shifted.data_ptr() % 16 != 0
+    actual = torch.ops.lowbitlinear_cute_w4a16.gemm(shifted, packed, scales, zeros)
+    torch.testing.assert_close(actual.cpu(), oracle_linear(x, packed, scales, zeros, mma=True), atol=ATOL, rtol=RTOL)

@@ -1,0 +1,127 @@
+"""N-split and K-split sharding.  The host logic runs as two gloo ranks on CPU; the GPU case
+runs the same check on two NCCL ranks when two GPUs are present."""
+import os
+import socket
+import sys
+from pathlib import Path
+
+import numpy as np
+import pytest
+import torch
+import torch.distributed as dist
+import torch.multiprocessing as mp
+
+ROOT = Path(__file__).resolve().parents[1]
+if str(ROOT) not in sys.path:
+    sys.path.insert(0, str(ROOT))
+
+from lowbitlinear_b200 import QuantizedLinear  # noqa: E402
+from lowbitlinear_b200.quantization import pack_int4, quantize_int4  # noqa: E402
+from lowbitlinear_b200.tensor_parallel import (  # noqa: E402
+    ColumnParallelLinear, RowParallelLinear, shard_column_parallel, shard_row_parallel)
+
+
+def _layer(n, k, seed, std=1.0):
+    g = torch.Generator("cpu").manual_seed(seed)
+    weight = (torch.randn(n, k, generator=g) * std).half()
+    x = torch.randn(3, k, generator=g).half()
+    return weight, x
+
+
+@pytest.mark.parametrize("world", [1, 2, 4, 8])
+def test_shards_equal_quantising_the_cut_weight(world):
+    """quantize(W)[shard] == quantize(W[shard]) bit for bit, for row cuts and for column cuts
+    on group boundaries."""
+    weight, _ = _layer(64, 1024, seed=1)
+    full = QuantizedLinear.from_float(weight)
+    for rank in range(world):
+        rows = slice(rank * 64 // world, (rank + 1) * 64 // world)
+        cols = slice(rank * 1024 // world, (rank + 1) * 1024 // world)
+        for shard, cut in ((shard_column_parallel(full, rank, world), weight[rows]),
+                           (shard_row_parallel(full, rank, world), weight[:, cols])):
+            direct = QuantizedLinear.from_float(cut.contiguous())
+            assert torch.equal(shard.packed_weight, direct.packed_weight)
+            assert torch.equal(shard.zeros, direct.zeros)
+            assert torch.equal(shard.scales, direct.scales)
+            assert shard.packed_weight.is_contiguous() and shard.scales.is_contiguous()
+
+
+def test_single_process_sharded_sum_matches_full():
+    weight, x = _layer(48, 512, seed=2)
+    full = QuantizedLinear.from_float(weight)
+    expected = full(x).float()
+    world = 4
+    column_blocks = [shard_column_parallel(full, r, world)(x) for r in range(world)]
+    assert torch.equal(torch.cat(column_blocks, dim=1), full(x))
+    partial = sum(shard_row_parallel(full, r, world)(x[:, r * 128:(r + 1) * 128].contiguous()).float()
+                  for r in range(world))
+    torch.testing.assert_close(partial, expected, atol=2e-2, rtol=2e-3)
+
+
+def test_invalid_splits():
+    full = QuantizedLinear.from_float(torch.randn(6, 192))
+    with pytest.raises(ValueError):
+        shard_column_parallel(full, 0, 4)
+    with pytest.raises(ValueError):
+        shard_row_parallel(full, 0, 2)  # 96 columns per rank is not a whole number of groups
+    shard_row_parallel(full, 0, 3)
+
+
+def _free_port():
+    with socket.socket() as s:
+        s.bind(("127.0.0.1", 0))
+        return s.getsockname()[1]
+
+
+def _worker(rank, world, port, backend, result_dir):
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
+    device = torch.device("cpu")
+    if backend == "nccl":
+        torch.cuda.set_device(rank)
+        device = torch.device("cuda", rank)
+    dist.init_process_group(backend, rank=rank, world_size=world)
+    try:
+        weight, x = _layer(256, 1024, seed=5, std=0.05)
+        full = QuantizedLinear.from_float(weight).to(device)
+        x = x.to(device)
+        expected = QuantizedLinear.from_float(weight)(x.cpu()).float()  # CPU reference path
+
+        column = ColumnParallelLinear.from_full(full, gather_output=True)
+        gathered = column(x)
+        local = ColumnParallelLinear.from_full(full)(x)
+        row = RowParallelLinear.from_full(full, input_is_parallel=False)
+        reduced = row(x)
+        part = 1024 // world
+        reduced_local = RowParallelLinear.from_full(full)(x[:, rank * part:(rank + 1) * part].contiguous())
+        np.savez(Path(result_dir) / f"rank{rank}.npz", gathered=gathered.float().cpu().numpy(),
+                 local=local.float().cpu().numpy(), reduced=reduced.float().cpu().numpy(),
+                 reduced_local=reduced_local.float().cpu().numpy(), expected=expected.numpy())
+    finally:
+        dist.destroy_process_group()
+
+
+def _check(result_dir, world):
+    for rank in range(world):
+        r = np.load(Path(result_dir) / f"rank{rank}.npz")
+        expected = r["expected"]
+        n_part = expected.shape[1] // world
+        np.testing.assert_allclose(r["gathered"], expected, atol=2e-3, rtol=1e-3)
+        np.testing.assert_allclose(r["local"], expected[:, rank * n_part:(rank + 1) * n_part], atol=2e-3, rtol=1e-3)
+        # FP16 partial sums are added across ranks: one extra FP16 rounding per rank.
+        np.testing.assert_allclose(r["reduced"], expected, atol=4e-3, rtol=2e-3)
+        np.testing.assert_allclose(r["reduced_local"], r["reduced"], atol=0, rtol=0)
+
+
+def test_two_gloo_ranks_on_cpu(tmp_path):
+    world = 2
+    mp.spawn(_worker, args=(world, _free_port(), "gloo", str(tmp_path)), nprocs=world, join=True)
+    _check(tmp_path, world)
+
+
+@pytest.mark.gpu
+def test_two_nccl_ranks_on_gpus(tmp_path):
+    if torch.cuda.device_count() < 2:
+        pytest.skip("needs two GPUs")
+    world = 2
+    mp.spawn(_worker, args=(world, _free_port(), "nccl", str(tmp_path)), nprocs=world, join=True)
+    _check(tmp_path, world)
