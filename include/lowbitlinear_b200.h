@@ -63,10 +63,11 @@ const char* lbl_last_error(void);
 int lbl_w4a16_select_path(int64_t M, int64_t N, int64_t K, int op);
 
 /* Bytes of scratch the given path (or LBL_PATH_AUTO) needs for this problem; 0 if none.
- * The scratch holds split-K partial sums followed by one arrival counter per row tile.
- * The counters must be zero before the first call that uses the buffer
- * (lbl_w4a16_workspace_init) and every call leaves them zero again, so one buffer can be
- * reused by successive calls on the same stream. */
+ * The scratch starts with a fixed 64 KiB region of arrival counters (one per 16-row tile),
+ * followed by the split-K partial sums.  The buffer must be zero before the first call that
+ * uses it (lbl_w4a16_workspace_init); every call leaves the counters zero again and the
+ * counter region never moves, so one buffer can be reused by successive calls, of any
+ * shape, on the same stream.  Calls that overlap on the GPU need separate buffers. */
 size_t lbl_w4a16_workspace_bytes(int64_t M, int64_t N, int64_t K, int path);
 
 /* Zero a scratch buffer on `stream` (asynchronous). */

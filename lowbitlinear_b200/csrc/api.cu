@@ -183,8 +183,8 @@ int run_linear(const void* X, const int32_t* packed_w, const float* scales, cons
           return fail(LBL_ERR_WORKSPACE, "split-K needs %zu bytes of scratch, got %zu", need, workspace_bytes);
         }
         if (!aligned16(workspace)) return fail(LBL_ERR_INVALID, "workspace must be 16-byte aligned");
-        partials = static_cast<float*>(workspace);
-        tickets = reinterpret_cast<int*>(static_cast<char*>(workspace) + plan.partial_bytes);
+        tickets = static_cast<int*>(workspace);
+        partials = reinterpret_cast<float*>(static_cast<char*>(workspace) + plan.ticket_bytes);
       }
       path = plan.nsplit > 1 ? LBL_PATH_GEMV_SPLITK : LBL_PATH_GEMV;
       err = lbl::launch_skinny(prob, plan, partials, tickets, info.status_word,

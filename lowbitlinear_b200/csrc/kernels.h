@@ -31,10 +31,16 @@ struct SkinnyPlan {
   int smem_bytes;   // dynamic shared memory per CTA
   int row_tiles;    // ceil(N / 16)
   size_t partial_bytes;  // split-K partial sums (0 when nsplit == 1)
-  size_t ticket_bytes;   // one int per row tile (0 when nsplit == 1)
+  size_t ticket_bytes;   // arrival counters (0 when nsplit == 1, else kSkinnyTicketBytes)
 };
 
 constexpr int kSkinnyMaxM = 32;
+// Split-K scratch layout: a fixed region of arrival counters (one int per 16-row tile) at the
+// start, partial sums behind it.  The counter region never moves, whatever the problem, so a
+// buffer that was zeroed once stays valid for every later call: counters are left at zero by
+// each kernel and partial sums need no initial value.
+constexpr size_t kSkinnyTicketBytes = 64 * 1024;
+constexpr int kSkinnyMaxSplitRowTiles = static_cast<int>(kSkinnyTicketBytes / sizeof(int));
 
 // True when the skinny kernel can serve the shape (M <= 32, K a multiple of 256).
 bool skinny_supports(int64_t M, int64_t N, int64_t K);

@@ -414,6 +414,7 @@ bool skinny_make_plan(int64_t M, int64_t N, int64_t K, int want_split, int sm_co
     if (chunks % d != 0) continue;
     const int kseg = k / d;
     if (kseg > kseg_cap) continue;
+    if (d > 1 && row_tiles > kSkinnyMaxSplitRowTiles) break;  // counters would not fit
     nsplit = d;
     if (forced > 0) {
       if (d >= forced) break;
@@ -463,7 +464,7 @@ bool skinny_make_plan(int64_t M, int64_t N, int64_t K, int want_split, int sm_co
   plan->smem_bytes = fixed + slots * slot_bytes;
   plan->row_tiles = row_tiles;
   plan->partial_bytes = nsplit > 1 ? static_cast<size_t>(nsplit) * M * N * sizeof(float) : 0;
-  plan->ticket_bytes = nsplit > 1 ? static_cast<size_t>(row_tiles) * sizeof(int) : 0;
+  plan->ticket_bytes = nsplit > 1 ? kSkinnyTicketBytes : 0;
   return units <= 0x7fffffffLL;
 }
 

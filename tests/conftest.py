@@ -127,3 +127,14 @@ def assert_north_star_parity(actual, expected):
     assert rel_l2 <= 1e-3, f"relative L2 error {rel_l2:.3e}"
     worst = ((a - e).abs() - (1e-2 + 1e-2 * e.abs())).max().item()
     assert worst <= 0, f"element outside 1e-2 + 1e-2|y| by {worst:.3e}"
+
+
+def expected_for_operator(x, packed, scales, zeros):
+    """Oracle output for the any-shape operator.  Shapes that its dispatcher hands to the
+    streaming kernel keep the FP32 scale (the reference-path semantics); the tensor-core and
+    masked kernels round each dequantised weight to FP16 first, as the reference GEMM does."""
+    from lowbitlinear_b200 import _ops
+
+    path = _ops.select_path(x.shape[0], packed.shape[0], x.shape[1])
+    fp32_scale = path in (_ops.PATH_GEMV, _ops.PATH_GEMV_SPLITK)
+    return oracle_linear(x, packed, scales, zeros, mma=not fp32_scale)

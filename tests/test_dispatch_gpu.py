@@ -6,7 +6,7 @@ import pytest
 import torch
 
 import lowbitlinear_b200.linear as linear_module
-from conftest import ATOL, RTOL, oracle_linear
+from conftest import ATOL, RTOL, expected_for_operator, oracle_linear
 from lowbitlinear_b200 import QuantizedLinear
 
 pytestmark = pytest.mark.gpu
@@ -20,7 +20,10 @@ pytestmark = pytest.mark.gpu
 def test_cuda_dispatch_executes_selected_operator(m, n, k, route, cuda_ops, monkeypatch):
     layer = QuantizedLinear.from_float(torch.randn(n, k, device=cuda_ops, dtype=torch.float16))
     x = torch.randn(m, k, device=cuda_ops, dtype=torch.float16)
-    expected = oracle_linear(x, layer.packed_weight, layer.scales, layer.zeros, mma=route == "gemm")
+    if route == "gemm":
+        expected = expected_for_operator(x, layer.packed_weight, layer.scales, layer.zeros)
+    else:
+        expected = oracle_linear(x, layer.packed_weight, layer.scales, layer.zeros)
     gemv = Mock(wraps=torch.ops.lowbitlinear_ext.w4a16_gemv_warp_vec)
     gemm = Mock(wraps=torch.ops.lowbitlinear_cute_w4a16.gemm)
     monkeypatch.setattr(torch.ops.lowbitlinear_ext, "w4a16_gemv_warp_vec", gemv)

@@ -86,8 +86,8 @@ def test_dispatcher_choices_and_scratch_sizes():
         assert name(2048, 129, 4096) == "generic"
         ws = _ops._lib.lbl_w4a16_workspace_bytes
         assert ws(1, 6144, 4096, _ops.PATH_AUTO) == 0
-        # nsplit * M * N floats + one counter per 16-row tile
-        assert ws(1, 4096, 4096, _ops.PATH_AUTO) == 2 * 4096 * 4 + 256 * 4
+        # fixed 64 KiB of arrival counters + nsplit * M * N floats
+        assert ws(1, 4096, 4096, _ops.PATH_AUTO) == 64 * 1024 + 2 * 4096 * 4
         assert ws(2048, 24576, 4096, _ops.PATH_AUTO) == 0
     finally:
         for k, v in env_backup.items():
