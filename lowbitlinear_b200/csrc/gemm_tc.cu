@@ -27,8 +27,7 @@
 // Shapes: N % 256 == 0 and K % 256 == 0; any M >= 1.  No cluster launch, no multicast.
 #include "common.cuh"
 #include "kernels.h"
-
-#include <cuda.h>
+#include "tensor_map.h"
 
 namespace lbl {
 namespace {
@@ -66,15 +65,6 @@ struct GemmParams {
 };
 
 // ---- tcgen05 / TMA wrappers -------------------------------------------------------------------
-__device__ __forceinline__ void tma_load_2d(void* smem_dst, const CUtensorMap* map, int c0, int c1,
-                                            uint64_t* bar) {
-  asm volatile(
-      "cp.async.bulk.tensor.2d.shared::cluster.global.tile.mbarrier::complete_tx::bytes "
-      "[%0], [%1, {%2, %3}], [%4];" ::"r"(smem_addr(smem_dst)),
-      "l"(map), "r"(c0), "r"(c1), "r"(smem_addr(bar))
-      : "memory");
-}
-
 __device__ __forceinline__ void tmem_alloc(uint32_t* smem_result, uint32_t cols) {
   asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(
                    smem_addr(smem_result)),
@@ -370,25 +360,6 @@ __global__ void __launch_bounds__(kThreads, 1)
   }
 }
 
-using EncodeTiledFn = CUresult (*)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*,
-                                   const cuuint64_t*, const cuuint64_t*, const cuuint32_t*,
-                                   const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
-                                   CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
-
-EncodeTiledFn encode_tiled_entry() {
-  static EncodeTiledFn fn = []() -> EncodeTiledFn {
-    void* ptr = nullptr;
-    cudaDriverEntryPointQueryResult query;
-    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &ptr, cudaEnableDefault, &query) !=
-            cudaSuccess ||
-        query != cudaDriverEntryPointSuccess) {
-      return nullptr;
-    }
-    return reinterpret_cast<EncodeTiledFn>(ptr);
-  }();
-  return fn;
-}
-
 }  // namespace
 
 bool gemm_tc_supports(int64_t M, int64_t N, int64_t K) {
@@ -397,19 +368,14 @@ bool gemm_tc_supports(int64_t M, int64_t N, int64_t K) {
 }
 
 cudaError_t launch_gemm_tc(const Problem& p, int* status_word, cudaStream_t stream) {
-  EncodeTiledFn encode = encode_tiled_entry();
-  if (encode == nullptr) return cudaErrorNotSupported;
-
   CUtensorMap tmap;
-  const cuuint64_t dims[2] = {static_cast<cuuint64_t>(p.K), static_cast<cuuint64_t>(p.M)};
-  const cuuint64_t strides[1] = {static_cast<cuuint64_t>(p.K) * sizeof(__half)};
-  const cuuint32_t box[2] = {kBK, kBM};
-  const cuuint32_t elem_strides[2] = {1, 1};
-  const CUresult rc = encode(&tmap, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2,
-                             const_cast<__half*>(p.x), dims, strides, box, elem_strides,
-                             CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
-                             CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
-  if (rc != CUDA_SUCCESS) return cudaErrorInvalidValue;
+  const uint64_t dims[2] = {static_cast<uint64_t>(p.K), static_cast<uint64_t>(p.M)};
+  const uint64_t strides[1] = {static_cast<uint64_t>(p.K) * sizeof(__half)};
+  const uint32_t box[2] = {kBK, kBM};
+  if (!encode_tensor_map(&tmap, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, p.x, dims, strides, box,
+                         CU_TENSOR_MAP_SWIZZLE_128B)) {
+    return cudaErrorInvalidValue;
+  }
 
   static bool configured[64] = {};
   int device = 0;

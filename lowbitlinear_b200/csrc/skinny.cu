@@ -28,9 +28,11 @@
 // ticket counter back to zero.  Results are bit-reproducible from run to run.
 #include "common.cuh"
 #include "kernels.h"
+#include "tensor_map.h"
 
 #include <algorithm>
 #include <cstdlib>
+#include <type_traits>
 
 namespace lbl {
 namespace {
@@ -48,9 +50,6 @@ constexpr int kSmemBudgetOneCta = 200 * 1024;
 
 struct KernelParams {
   const __half* x;
-  const uint8_t* packed;  // byte view of the packed words
-  const uint8_t* scales;  // byte view
-  const uint8_t* zeros;   // byte view
   __half* y;
   float* partials;
   int* tickets;
@@ -129,7 +128,10 @@ __device__ __forceinline__ void build_activation_operand(const KernelParams& p, 
 }
 
 template <int NT>
-__global__ void __launch_bounds__(kThreads, (NT <= 2 ? 2 : 1)) w4a16_skinny_kernel(const KernelParams p) {
+__global__ void __launch_bounds__(kThreads, (NT <= 2 ? 2 : 1))
+    w4a16_skinny_kernel(const __grid_constant__ CUtensorMap tmap_w,
+                        const __grid_constant__ CUtensorMap tmap_s,
+                        const __grid_constant__ CUtensorMap tmap_z, const KernelParams p) {
   constexpr int MC = 8 * NT;
   extern __shared__ __align__(128) uint8_t smem[];
   Header* hdr = reinterpret_cast<Header*>(smem);
@@ -155,8 +157,6 @@ __global__ void __launch_bounds__(kThreads, (NT <= 2 ? 2 : 1)) w4a16_skinny_kern
   // The next kernel in the stream may start filling its own ring as soon as it finds room.
   pdl_allow_next_kernel();
 
-  const int meta_bytes = p.stage_k / 16;  // bytes of one row's scales (or zeros) per stage
-  const int packed_bytes = p.stage_k / 2;
   const int zeros_block = kRows * p.packed_pitch + kRows * p.meta_pitch;
 
   if (warp == kConsumerWarps) {
@@ -166,7 +166,6 @@ __global__ void __launch_bounds__(kThreads, (NT <= 2 ? 2 : 1)) w4a16_skinny_kern
       const int ks = unit / p.row_tiles;
       const int rt = unit - ks * p.row_tiles;
       const int n0 = rt * kRows;
-      const int rows = min(kRows, p.N - n0);
       for (int st = 0; st < p.stages_per_unit; ++st, ++it) {
         const int slot = it % p.slots;
         const int round = it / p.slots;
@@ -175,21 +174,17 @@ __global__ void __launch_bounds__(kThreads, (NT <= 2 ? 2 : 1)) w4a16_skinny_kern
                             kStatusSkinnyEmptyWait);
         }
         if (*abort_flag) break;
-        const int k0 = ks * p.kseg + st * p.stage_k;
+        // Stage index along K: the tensor maps view every row as [K / stage_k][stage_k].
+        const int stage_index = ks * p.stages_per_unit + st;
         if (lane == 0) {
-          mbar_arrive_expect_tx(&hdr->full[slot],
-                                static_cast<uint32_t>(rows * (packed_bytes + 2 * meta_bytes)));
-        }
-        __syncwarp();
-        if (lane < rows) {
+          // Three tiled copies per stage; each box is 16 rows by (stage columns + padding), the
+          // padding lies outside the tensor's inner extent and is zero-filled without traffic,
+          // as are rows past N.  A box always counts its full size on the barrier.
           uint8_t* base = ring + static_cast<size_t>(slot) * p.slot_bytes;
-          const size_t row = static_cast<size_t>(n0 + lane);
-          bulk_load(base + lane * p.packed_pitch, p.packed + row * (p.K / 2) + k0 / 2,
-                    packed_bytes, &hdr->full[slot]);
-          bulk_load(base + kRows * p.packed_pitch + lane * p.meta_pitch,
-                    p.scales + row * (p.K / 16) + k0 / 16, meta_bytes, &hdr->full[slot]);
-          bulk_load(base + zeros_block + lane * p.meta_pitch,
-                    p.zeros + row * (p.K / 16) + k0 / 16, meta_bytes, &hdr->full[slot]);
+          mbar_arrive_expect_tx(&hdr->full[slot], static_cast<uint32_t>(p.slot_bytes));
+          tma_load_3d(base, &tmap_w, 0, stage_index, n0, &hdr->full[slot]);
+          tma_load_3d(base + kRows * p.packed_pitch, &tmap_s, 0, stage_index, n0, &hdr->full[slot]);
+          tma_load_3d(base + zeros_block, &tmap_z, 0, stage_index, n0, &hdr->full[slot]);
         }
       }
       if (*abort_flag) break;
@@ -239,65 +234,91 @@ __global__ void __launch_bounds__(kThreads, (NT <= 2 ? 2 : 1)) w4a16_skinny_kern
       const int* zp_a = reinterpret_cast<const int*>(base + zeros_block + g * p.meta_pitch);
       const int* zp_b = reinterpret_cast<const int*>(base + zeros_block + (g + 8) * p.meta_pitch);
 
-      for (int G = warp; G < groups_per_stage; G += kConsumerWarps) {
-        const uint2 wa = *reinterpret_cast<const uint2*>(row_a + G * 32);
-        const uint2 wb = *reinterpret_cast<const uint2*>(row_b + G * 32);
-        const float scale_a = sc_a[G];
-        const float scale_b = sc_b[G];
-        const float zero_a = static_cast<float>(zp_a[G]);
-        const float zero_b = static_cast<float>(zp_b[G]);
-
-        uint32_t ha[8], hb[8];
-        {
-          uint32_t q[4];
-          nibbles_as_subnormal_half2(wa.x, q);
-          ha[0] = q[0]; ha[1] = q[1]; ha[2] = q[2]; ha[3] = q[3];
-          nibbles_as_subnormal_half2(wa.y, q);
-          ha[4] = q[0]; ha[5] = q[1]; ha[6] = q[2]; ha[7] = q[3];
-          nibbles_as_subnormal_half2(wb.x, q);
-          hb[0] = q[0]; hb[1] = q[1]; hb[2] = q[2]; hb[3] = q[3];
-          nibbles_as_subnormal_half2(wb.y, q);
-          hb[4] = q[0]; hb[5] = q[1]; hb[6] = q[2]; hb[7] = q[3];
+      // U groups are processed together and every group runs two MMA chains (steps 0-1 and
+      // steps 2-3), so that 2 U independent tensor-core instructions are in flight per warp.
+      auto run_groups = [&](auto u_tag, int G0) {
+        constexpr int U = decltype(u_tag)::value;
+        uint2 wa[U], wb[U];
+        float scale_a[U], scale_b[U], zero_a[U], zero_b[U];
+#pragma unroll
+        for (int u = 0; u < U; ++u) {
+          const int G = G0 + u * kConsumerWarps;
+          wa[u] = *reinterpret_cast<const uint2*>(row_a + G * 32);
+          wb[u] = *reinterpret_cast<const uint2*>(row_b + G * 32);
+          scale_a[u] = sc_a[G];
+          scale_b[u] = sc_b[G];
+          zero_a[u] = static_cast<float>(zp_a[G]);
+          zero_b[u] = static_cast<float>(zp_b[G]);
         }
-
-        const int group_in_seg = st * groups_per_stage + G;
-        const uint2* xf_group = xf + static_cast<size_t>(group_in_seg) * 4 * p.M * 4;
-        float d[NT][4];
+        uint32_t ha[U][8], hb[U][8];
 #pragma unroll
-        for (int s = 0; s < 4; ++s) {
-          const uint32_t a[4] = {ha[2 * s], hb[2 * s], ha[2 * s + 1], hb[2 * s + 1]};
+        for (int u = 0; u < U; ++u) {
+          uint32_t q[4];
+          nibbles_as_subnormal_half2(wa[u].x, q);
+          ha[u][0] = q[0]; ha[u][1] = q[1]; ha[u][2] = q[2]; ha[u][3] = q[3];
+          nibbles_as_subnormal_half2(wa[u].y, q);
+          ha[u][4] = q[0]; ha[u][5] = q[1]; ha[u][6] = q[2]; ha[u][7] = q[3];
+          nibbles_as_subnormal_half2(wb[u].x, q);
+          hb[u][0] = q[0]; hb[u][1] = q[1]; hb[u][2] = q[2]; hb[u][3] = q[3];
+          nibbles_as_subnormal_half2(wb[u].y, q);
+          hb[u][4] = q[0]; hb[u][5] = q[1]; hb[u][6] = q[2]; hb[u][7] = q[3];
+        }
+        float d[U][2][NT][4];
 #pragma unroll
-          for (int nt = 0; nt < NT; ++nt) {
-            const int n = nt * 8 + g;
-            uint2 b = make_uint2(0u, 0u);
-            if (n < p.M) b = xf_group[(s * p.M + n) * 4 + t];
-            if (s == 0) {
-              mma_m16n8k16(d[nt], a, b.x, b.y, zero4);
-            } else {
-              mma_m16n8k16(d[nt], a, b.x, b.y, d[nt]);
+        for (int j = 0; j < 2; ++j) {
+#pragma unroll
+          for (int c = 0; c < 2; ++c) {
+            const int s = 2 * c + j;  // chain c covers steps 2c and 2c + 1
+#pragma unroll
+            for (int u = 0; u < U; ++u) {
+              const int group_in_seg = st * groups_per_stage + G0 + u * kConsumerWarps;
+              const uint2* xf_step = xf + (static_cast<size_t>(group_in_seg) * 4 + s) * p.M * 4 + t;
+              const uint32_t a[4] = {ha[u][2 * s], hb[u][2 * s], ha[u][2 * s + 1], hb[u][2 * s + 1]};
+#pragma unroll
+              for (int nt = 0; nt < NT; ++nt) {
+                const int n = nt * 8 + g;
+                uint2 b = make_uint2(0u, 0u);
+                if (n < p.M) b = xf_step[n * 4];
+                if (j == 0) {
+                  mma_m16n8k16(d[u][c][nt], a, b.x, b.y, zero4);
+                } else {
+                  mma_m16n8k16(d[u][c][nt], a, b.x, b.y, d[u][c][nt]);
+                }
+              }
             }
           }
         }
-
         // acc += scale * (sum q x) - (scale * zero) * (sum x); the MMA result carries the
-        // factor kNibbleUnit^-1 of the nibble encoding.
-        const float fa = scale_a * kNibbleUnit;
-        const float fb = scale_b * kNibbleUnit;
-        const float ca = -(scale_a * zero_a);
-        const float cb = -(scale_b * zero_b);
+        // factor 1 / kNibbleUnit of the nibble encoding.
 #pragma unroll
-        for (int nt = 0; nt < NT; ++nt) {
-          const float2 sums =
-              *reinterpret_cast<const float2*>(sx + group_in_seg * MC + nt * 8 + 2 * t);
-          acc[nt][0] = fmaf(fa, d[nt][0], acc[nt][0]);
-          acc[nt][1] = fmaf(fa, d[nt][1], acc[nt][1]);
-          acc[nt][2] = fmaf(fb, d[nt][2], acc[nt][2]);
-          acc[nt][3] = fmaf(fb, d[nt][3], acc[nt][3]);
-          acc[nt][0] = fmaf(ca, sums.x, acc[nt][0]);
-          acc[nt][1] = fmaf(ca, sums.y, acc[nt][1]);
-          acc[nt][2] = fmaf(cb, sums.x, acc[nt][2]);
-          acc[nt][3] = fmaf(cb, sums.y, acc[nt][3]);
+        for (int u = 0; u < U; ++u) {
+          const int group_in_seg = st * groups_per_stage + G0 + u * kConsumerWarps;
+          const float fa = scale_a[u] * kNibbleUnit;
+          const float fb = scale_b[u] * kNibbleUnit;
+          const float ca = -(scale_a[u] * zero_a[u]);
+          const float cb = -(scale_b[u] * zero_b[u]);
+#pragma unroll
+          for (int nt = 0; nt < NT; ++nt) {
+            const float2 sums =
+                *reinterpret_cast<const float2*>(sx + group_in_seg * MC + nt * 8 + 2 * t);
+            acc[nt][0] = fmaf(fa, d[u][0][nt][0] + d[u][1][nt][0], acc[nt][0]);
+            acc[nt][1] = fmaf(fa, d[u][0][nt][1] + d[u][1][nt][1], acc[nt][1]);
+            acc[nt][2] = fmaf(fb, d[u][0][nt][2] + d[u][1][nt][2], acc[nt][2]);
+            acc[nt][3] = fmaf(fb, d[u][0][nt][3] + d[u][1][nt][3], acc[nt][3]);
+            acc[nt][0] = fmaf(ca, sums.x, acc[nt][0]);
+            acc[nt][1] = fmaf(ca, sums.y, acc[nt][1]);
+            acc[nt][2] = fmaf(cb, sums.x, acc[nt][2]);
+            acc[nt][3] = fmaf(cb, sums.y, acc[nt][3]);
+          }
         }
+      };
+      constexpr int kUnroll = NT == 1 ? 2 : 1;
+      int G = warp;
+      for (; G + (kUnroll - 1) * kConsumerWarps < groups_per_stage; G += kUnroll * kConsumerWarps) {
+        run_groups(std::integral_constant<int, kUnroll>{}, G);
+      }
+      for (; G < groups_per_stage; G += kConsumerWarps) {
+        run_groups(std::integral_constant<int, 1>{}, G);
       }
       __syncwarp();
       if (lane == 0) mbar_arrive(&hdr->empty[slot]);
@@ -360,8 +381,8 @@ int env_int(const char* name, int fallback) {
 }
 
 template <int NT>
-cudaError_t launch_nt(const KernelParams& kp, const SkinnyPlan& plan, bool pdl,
-                      cudaStream_t stream) {
+cudaError_t launch_nt(const CUtensorMap (&maps)[3], const KernelParams& kp, const SkinnyPlan& plan,
+                      bool pdl, cudaStream_t stream) {
   // The opt-in to large dynamic shared memory is per device and per kernel; repeating it is
   // harmless, so a racy "done" flag is enough.
   static bool configured[64] = {};
@@ -384,7 +405,7 @@ cudaError_t launch_nt(const KernelParams& kp, const SkinnyPlan& plan, bool pdl,
   attr[0].val.programmaticStreamSerializationAllowed = 1;
   cfg.attrs = attr;
   cfg.numAttrs = pdl ? 1 : 0;
-  return cudaLaunchKernelEx(&cfg, w4a16_skinny_kernel<NT>, kp);
+  return cudaLaunchKernelEx(&cfg, w4a16_skinny_kernel<NT>, maps[0], maps[1], maps[2], kp);
 }
 
 }  // namespace
@@ -406,7 +427,7 @@ bool skinny_make_plan(int64_t M, int64_t N, int64_t K, int want_split, int sm_co
 
   // Candidate splits: every divisor d of K / 256 gives kseg = K / d.
   const int kseg_cap = std::max(256, (kXfBudgetBytes / (2 * m)) / 256 * 256);
-  const int target_units = 2 * sm_count;
+  const int target_units = sm_count;  // split K only when the row tiles cannot fill the SMs
   int forced = env_int("LBL_SKINNY_NSPLIT", 0);
   if (want_split > 0) forced = want_split;
   int nsplit = 0;
@@ -475,9 +496,6 @@ cudaError_t launch_skinny(const Problem& p, const SkinnyPlan& plan, float* parti
   const int mc = 8 * nt;
   KernelParams kp;
   kp.x = p.x;
-  kp.packed = reinterpret_cast<const uint8_t*>(p.packed);
-  kp.scales = reinterpret_cast<const uint8_t*>(p.scales);
-  kp.zeros = reinterpret_cast<const uint8_t*>(p.zeros);
   kp.y = p.y;
   kp.partials = partials;
   kp.tickets = tickets;
@@ -499,13 +517,43 @@ cudaError_t launch_skinny(const Problem& p, const SkinnyPlan& plan, float* parti
   kp.red_offset = kp.sx_offset + (plan.kseg / 64) * mc * 4;
   kp.xf_offset = kp.red_offset + kConsumerWarps * kRows * mc * 4;
   kp.ring_offset = kp.xf_offset + m * plan.kseg * 2;
+  // Tensor maps over the reference layout.  Each row is viewed as [K / stage_k][stage_k]; a box
+  // takes 16 rows of one stage plus 4 elements of padding per row.  The padding is outside the
+  // inner extent, so it is zero-filled and costs no traffic, and it gives the rows in shared
+  // memory the pitch (stage bytes + 32 resp. + 16) that keeps the fragment loads free of
+  // bank conflicts.
+  CUtensorMap maps[3];
+  const uint64_t stages_in_row = static_cast<uint64_t>(p.K / plan.stage_k);
+  const uint64_t n_rows = static_cast<uint64_t>(p.N);
+  {
+    const uint64_t dims[3] = {static_cast<uint64_t>(plan.stage_k / 16), stages_in_row, n_rows};
+    const uint64_t strides[2] = {static_cast<uint64_t>(plan.stage_k / 2),
+                                 static_cast<uint64_t>(p.K / 2)};
+    const uint32_t box[3] = {static_cast<uint32_t>(plan.stage_k / 16 + 4), 1, kRows};
+    if (!encode_tensor_map(&maps[0], CU_TENSOR_MAP_DATA_TYPE_UINT64, 3, p.packed, dims, strides, box,
+                           CU_TENSOR_MAP_SWIZZLE_NONE)) {
+      return cudaErrorInvalidValue;
+    }
+  }
+  {
+    const uint64_t dims[3] = {static_cast<uint64_t>(plan.stage_k / 64), stages_in_row, n_rows};
+    const uint64_t strides[2] = {static_cast<uint64_t>(plan.stage_k / 16),
+                                 static_cast<uint64_t>(p.K / 16)};
+    const uint32_t box[3] = {static_cast<uint32_t>(plan.stage_k / 64 + 4), 1, kRows};
+    if (!encode_tensor_map(&maps[1], CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 3, p.scales, dims, strides, box,
+                           CU_TENSOR_MAP_SWIZZLE_NONE) ||
+        !encode_tensor_map(&maps[2], CU_TENSOR_MAP_DATA_TYPE_INT32, 3, p.zeros, dims, strides, box,
+                           CU_TENSOR_MAP_SWIZZLE_NONE)) {
+      return cudaErrorInvalidValue;
+    }
+  }
   switch (nt) {
     case 1:
-      return launch_nt<1>(kp, plan, pdl, stream);
+      return launch_nt<1>(maps, kp, plan, pdl, stream);
     case 2:
-      return launch_nt<2>(kp, plan, pdl, stream);
+      return launch_nt<2>(maps, kp, plan, pdl, stream);
     default:
-      return launch_nt<4>(kp, plan, pdl, stream);
+      return launch_nt<4>(maps, kp, plan, pdl, stream);
   }
 }
 

@@ -75,8 +75,9 @@ def test_dispatcher_choices_and_scratch_sizes():
         # Decode shapes stream; a small N or a long K is split across CTAs.
         assert name(1, 6144, 4096) == "gemv"
         assert name(1, 24576, 4096) == "gemv"
-        assert name(1, 4096, 4096) == "gemv_splitk"
-        assert name(1, 4096, 12288) == "gemv_splitk"
+        assert name(1, 4096, 4096) == "gemv"
+        assert name(1, 4096, 12288) == "gemv"
+        assert name(1, 512, 4096) == "gemv_splitk"     # a tensor-parallel shard: 32 row tiles
         assert name(8, 4096, 12288) == "gemv_splitk"   # activations of one segment must fit on chip
         # Prefill shapes go to the tensor cores; ragged shapes to the masked kernel.
         assert name(2048, 24576, 4096) == "gemm_tc"
@@ -87,7 +88,8 @@ def test_dispatcher_choices_and_scratch_sizes():
         ws = _ops._lib.lbl_w4a16_workspace_bytes
         assert ws(1, 6144, 4096, _ops.PATH_AUTO) == 0
         # fixed 64 KiB of arrival counters + nsplit * M * N floats
-        assert ws(1, 4096, 4096, _ops.PATH_AUTO) == 64 * 1024 + 2 * 4096 * 4
+        assert ws(1, 4096, 4096, _ops.PATH_AUTO) == 0
+        assert ws(1, 512, 4096, _ops.PATH_AUTO) == 64 * 1024 + 4 * 512 * 4
         assert ws(2048, 24576, 4096, _ops.PATH_AUTO) == 0
     finally:
         for k, v in env_backup.items():
