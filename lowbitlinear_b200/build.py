@@ -21,7 +21,7 @@ CSRC = PACKAGE_DIR / "csrc"
 INCLUDE = PACKAGE_DIR.parent / "include"
 OUTPUT = PACKAGE_DIR / "_C.so"
 BUILD_DIR = PACKAGE_DIR / "build"
-SOURCES = ("api.cu", "generic.cu", "skinny.cu", "gemm_tc.cu", "tensor_map.cu")
+SOURCES = ("api.cu", "generic.cu", "skinny.cu", "gemv_decode.cu", "gemm_tc.cu", "tensor_map.cu")
 ARCH_FLAGS = ("-gencode", "arch=compute_100a,code=sm_100a")
 COMMON_FLAGS = ("-O3", "-std=c++17", "-lineinfo", "-Xcompiler", "-fPIC", "-Xptxas", "-v")
 

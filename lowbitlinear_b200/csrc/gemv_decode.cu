@@ -1,0 +1,351 @@
+// Decode GEMV (M <= 2): the instruction-lean form of the streaming kernel in skinny.cu.
+//
+// Same data movement as skinny.cu -- persistent CTAs, one producer warp, a ring of stages filled
+// by three tiled TMA copies each (packed words, scales, zero points of 16 rows), optional split-K
+// with an ordered reduction -- but the warp MMA is used differently.  With at most two rows of
+// activations, six of the eight B columns of an m16n8k16 MMA would be idle.  Here they separate
+// the four lanes of a quad instead: column n of B holds the activations of the k-slots owned by
+// lane n of the quad and zeros elsewhere, so one MMA yields, per weight row, four partial sums
+// that belong to four different 32-column pieces of K.  Each lane can therefore read 16 bytes
+// (32 weights) of its row with a single shared-memory load, and eight MMAs consume 16 rows by
+// 128 columns (two quantisation groups) with
+//     2 loads of weights, 40 integer instructions of nibble extraction, 8 MMAs,
+//     4 predicated loads of activations and about 20 instructions of FP32 scale / zero point,
+// roughly a third of the instructions per weight of the general kernel.  Columns 4-7 carry the
+// second activation row when M = 2.
+//
+// Numerics are those of skinny.cu: raw levels q as exact FP16 subnormals, FP32 accumulation,
+//     acc += scale * (sum_k q x - zero * sum_k x)   per group, in FP32.
+#include "common.cuh"
+#include "kernels.h"
+#include "tensor_map.h"
+
+namespace lbl {
+namespace {
+
+constexpr int kRows = 16;
+constexpr int kConsumerWarps = 8;
+constexpr int kConsumerThreads = kConsumerWarps * 32;
+constexpr int kThreads = kConsumerThreads + 32;
+constexpr int kMaxSlots = 8;
+constexpr int kHeaderBytes = 256;
+
+struct DecodeParams {
+  const __half* x;
+  __half* y;
+  float* partials;
+  int* tickets;
+  int* status;
+  int M, N, K;
+  int kseg, nsplit, stage_k, stages_per_unit, slots;
+  int row_tiles, units;
+  int packed_pitch, meta_pitch, slot_bytes;
+  int sx_offset, red_offset, xf_offset, ring_offset;
+};
+
+struct Header {
+  uint64_t full[kMaxSlots];
+  uint64_t empty[kMaxSlots];
+  int abort_flag;
+  int ticket;
+};
+static_assert(sizeof(Header) <= kHeaderBytes, "header does not fit");
+
+__device__ __forceinline__ uint32_t pack_half2(__half lo, __half hi) {
+  return static_cast<uint32_t>(__half_as_ushort(lo)) |
+         (static_cast<uint32_t>(__half_as_ushort(hi)) << 16);
+}
+
+// Activation operand of one K segment.  Word w of row m (columns 8w..8w+7) becomes the 16 bytes
+//   (x0, x4) (x1, x5)/16 (x2, x6) (x3, x7)/16
+// in the order the nibble extraction delivers the weights (odd nibbles carry a factor 16), at
+// xf[m * words + w]; sx[group * 2 + m] is the FP32 sum of the group's 64 activations.
+__device__ __forceinline__ void build_activation_operand(const DecodeParams& p, int k_begin,
+                                                         uint4* xf, float* sx, int tid) {
+  const int groups = p.kseg / 64;
+  const int words_seg = p.kseg / 8;
+  if (p.M < 2) {
+    for (int i = tid; i < groups; i += kConsumerThreads) sx[2 * i + 1] = 0.0f;
+  }
+  const __half sixteenth = __float2half_rn(0.0625f);
+  const int total = p.M * words_seg;  // multiple of 32
+  for (int idx = tid; idx < total; idx += kConsumerThreads) {
+    const int m = idx / words_seg;
+    const int wd = idx - m * words_seg;
+    const uint4 raw =
+        *reinterpret_cast<const uint4*>(p.x + static_cast<size_t>(m) * p.K + k_begin + wd * 8);
+    const __half2 v01 = *reinterpret_cast<const __half2*>(&raw.x);
+    const __half2 v23 = *reinterpret_cast<const __half2*>(&raw.y);
+    const __half2 v45 = *reinterpret_cast<const __half2*>(&raw.z);
+    const __half2 v67 = *reinterpret_cast<const __half2*>(&raw.w);
+    const __half x0 = __low2half(v01), x1 = __high2half(v01);
+    const __half x2 = __low2half(v23), x3 = __high2half(v23);
+    const __half x4 = __low2half(v45), x5 = __high2half(v45);
+    const __half x6 = __low2half(v67), x7 = __high2half(v67);
+    float sum = ((__half2float(x0) + __half2float(x1)) + (__half2float(x2) + __half2float(x3))) +
+                ((__half2float(x4) + __half2float(x5)) + (__half2float(x6) + __half2float(x7)));
+    sum += __shfl_xor_sync(0xffffffffu, sum, 1);
+    sum += __shfl_xor_sync(0xffffffffu, sum, 2);
+    sum += __shfl_xor_sync(0xffffffffu, sum, 4);
+    uint4 out;
+    out.x = pack_half2(x0, x4);
+    out.y = pack_half2(__hmul(x1, sixteenth), __hmul(x5, sixteenth));
+    out.z = pack_half2(x2, x6);
+    out.w = pack_half2(__hmul(x3, sixteenth), __hmul(x7, sixteenth));
+    xf[idx] = out;
+    if ((wd & 7) == 0) sx[(wd >> 3) * 2 + m] = sum;
+  }
+}
+
+__global__ void __launch_bounds__(kThreads, 2)
+    w4a16_gemv_decode_kernel(const __grid_constant__ CUtensorMap tmap_w,
+                             const __grid_constant__ CUtensorMap tmap_s,
+                             const __grid_constant__ CUtensorMap tmap_z, const DecodeParams p) {
+  extern __shared__ __align__(128) uint8_t smem[];
+  Header* hdr = reinterpret_cast<Header*>(smem);
+  float* sx = reinterpret_cast<float*>(smem + p.sx_offset);
+  float* red = reinterpret_cast<float*>(smem + p.red_offset);
+  uint4* xf = reinterpret_cast<uint4*>(smem + p.xf_offset);
+  uint8_t* ring = smem + p.ring_offset;
+  volatile int* abort_flag = &hdr->abort_flag;
+
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < p.slots; ++s) {
+      mbar_init(&hdr->full[s], 1);
+      mbar_init(&hdr->empty[s], kConsumerWarps);
+    }
+    hdr->abort_flag = 0;
+    hdr->ticket = 0;
+    mbar_init_fence();
+  }
+  __syncthreads();
+  // The next kernel in the stream may start filling its own ring as soon as it finds room.
+  pdl_allow_next_kernel();
+
+  const int scales_block = kRows * p.packed_pitch;
+  const int zeros_block = scales_block + kRows * p.meta_pitch;
+
+  if (warp == kConsumerWarps) {
+    // ------------------------------- producer ------------------------------------------------
+    if (lane == 0) {
+      int it = 0;
+      for (int unit = blockIdx.x; unit < p.units; unit += gridDim.x) {
+        const int ks = unit / p.row_tiles;
+        const int n0 = (unit - ks * p.row_tiles) * kRows;
+        for (int st = 0; st < p.stages_per_unit; ++st, ++it) {
+          const int slot = it % p.slots;
+          const int round = it / p.slots;
+          if (round > 0) {
+            mbar_wait_bounded(&hdr->empty[slot], (round - 1) & 1, abort_flag, p.status,
+                              kStatusSkinnyEmptyWait);
+          }
+          if (*abort_flag) return;
+          // The tensor maps view every row as [K / stage_k][stage_k (+ padding)]; padding and
+          // rows past N are zero-filled by the copy engine and cost no traffic.
+          const int stage_index = ks * p.stages_per_unit + st;
+          uint8_t* base = ring + static_cast<size_t>(slot) * p.slot_bytes;
+          mbar_arrive_expect_tx(&hdr->full[slot], static_cast<uint32_t>(p.slot_bytes));
+          tma_load_3d(base, &tmap_w, 0, stage_index, n0, &hdr->full[slot]);
+          tma_load_3d(base + scales_block, &tmap_s, 0, stage_index, n0, &hdr->full[slot]);
+          tma_load_3d(base + zeros_block, &tmap_z, 0, stage_index, n0, &hdr->full[slot]);
+        }
+      }
+    }
+    return;
+  }
+
+  // --------------------------------- consumers -----------------------------------------------
+  const int tid = threadIdx.x;  // 0..255
+  const int g = lane >> 2;
+  const int t = lane & 3;
+  // B operand: column n = g of this lane carries activation row n / 4 for the k-slots of quad
+  // lane n % 4, so only lanes with g % 4 == t hold activations; the others hold zeros.
+  const int feed_row = g >> 2;
+  const bool feeds_b = ((g & 3) == t) && (feed_row < p.M);
+  // D result: this lane's columns 2t, 2t+1 are the two halves of group (t & 1) of the macro
+  // tile, for activation row t / 2.
+  const int out_row = t >> 1;
+  const int group_parity = t & 1;
+  const int macro_per_stage = p.stage_k / 128;
+  const int words_seg = p.kseg / 8;
+  const float zero4[4] = {0.0f, 0.0f, 0.0f, 0.0f};
+
+  int it = 0;
+  int current_ks = -1;
+  for (int unit = blockIdx.x; unit < p.units; unit += gridDim.x) {
+    const int ks = unit / p.row_tiles;
+    const int rt = unit - ks * p.row_tiles;
+    const int n0 = rt * kRows;
+
+    if (ks != current_ks) {
+      // Activations are the only input the previous kernel may have produced.
+      if (current_ks < 0) pdl_wait_for_previous_kernel();
+      build_activation_operand(p, ks * p.kseg, xf, sx, tid);
+      named_barrier(1, kConsumerThreads);
+      current_ks = ks;
+    }
+
+    float acc_a = 0.0f;  // row n0 + g
+    float acc_b = 0.0f;  // row n0 + g + 8
+    for (int st = 0; st < p.stages_per_unit; ++st, ++it) {
+      const int slot = it % p.slots;
+      const int round = it / p.slots;
+      mbar_wait_bounded(&hdr->full[slot], round & 1, abort_flag, p.status, kStatusSkinnyFullWait);
+
+      const uint8_t* base = ring + static_cast<size_t>(slot) * p.slot_bytes;
+      const uint8_t* row_a = base + g * p.packed_pitch + t * 16;
+      const uint8_t* row_b = row_a + 8 * p.packed_pitch;
+      const float* sc_a = reinterpret_cast<const float*>(base + scales_block + g * p.meta_pitch) + group_parity;
+      const float* sc_b = reinterpret_cast<const float*>(base + scales_block + (g + 8) * p.meta_pitch) + group_parity;
+      const int* zp_a = reinterpret_cast<const int*>(base + zeros_block + g * p.meta_pitch) + group_parity;
+      const int* zp_b = reinterpret_cast<const int*>(base + zeros_block + (g + 8) * p.meta_pitch) + group_parity;
+      const uint4* xf_lane = xf + feed_row * words_seg + st * (p.stage_k / 8) + t * 4;
+      const float* sx_lane = sx + (st * (p.stage_k / 64) + group_parity) * 2 + out_row;
+
+#pragma unroll 2
+      for (int j = warp; j < macro_per_stage; j += kConsumerWarps) {
+        const uint4 wa = *reinterpret_cast<const uint4*>(row_a + j * 64);
+        const uint4 wb = *reinterpret_cast<const uint4*>(row_b + j * 64);
+        uint4 xb[4];
+#pragma unroll
+        for (int i = 0; i < 4; ++i) xb[i] = make_uint4(0u, 0u, 0u, 0u);
+        if (feeds_b) {
+#pragma unroll
+          for (int i = 0; i < 4; ++i) xb[i] = xf_lane[j * 16 + i];
+        }
+        const float scale_a = sc_a[2 * j];
+        const float scale_b = sc_b[2 * j];
+        const float zero_a = static_cast<float>(zp_a[2 * j]);
+        const float zero_b = static_cast<float>(zp_b[2 * j]);
+        const float sum_x = sx_lane[4 * j];
+
+        const uint32_t words_a[4] = {wa.x, wa.y, wa.z, wa.w};
+        const uint32_t words_b[4] = {wb.x, wb.y, wb.z, wb.w};
+        float d0[4], d1[4];
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+          uint32_t qa[4], qb[4];
+          nibbles_as_subnormal_half2(words_a[i], qa);
+          nibbles_as_subnormal_half2(words_b[i], qb);
+          const uint32_t a0[4] = {qa[0], qb[0], qa[1], qb[1]};
+          const uint32_t a1[4] = {qa[2], qb[2], qa[3], qb[3]};
+          if (i == 0) {
+            mma_m16n8k16(d0, a0, xb[i].x, xb[i].y, zero4);
+            mma_m16n8k16(d1, a1, xb[i].z, xb[i].w, zero4);
+          } else {
+            mma_m16n8k16(d0, a0, xb[i].x, xb[i].y, d0);
+            mma_m16n8k16(d1, a1, xb[i].z, xb[i].w, d1);
+          }
+        }
+        // acc += scale * (sum q x) - (scale * zero) * (sum x); the MMA result carries the factor
+        // 1 / kNibbleUnit of the nibble encoding.
+        const float qx_a = (d0[0] + d0[1]) + (d1[0] + d1[1]);
+        const float qx_b = (d0[2] + d0[3]) + (d1[2] + d1[3]);
+        acc_a = fmaf(scale_a * kNibbleUnit, qx_a, acc_a);
+        acc_b = fmaf(scale_b * kNibbleUnit, qx_b, acc_b);
+        acc_a = fmaf(-(scale_a * zero_a), sum_x, acc_a);
+        acc_b = fmaf(-(scale_b * zero_b), sum_x, acc_b);
+      }
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&hdr->empty[slot]);
+    }
+
+    // ---- reduction of the unit over warps and over the two group parities, fixed order -------
+    red[(warp * kRows + g) * 4 + t] = acc_a;
+    red[(warp * kRows + g + 8) * 4 + t] = acc_b;
+    named_barrier(1, kConsumerThreads);
+    const int col = tid >> 4;  // activation row, valid for tid < 32
+    const int row = tid & 15;
+    if (tid < 2 * kRows) {
+      float v = 0.0f;
+#pragma unroll
+      for (int w = 0; w < kConsumerWarps; ++w) {
+        v += red[(w * kRows + row) * 4 + 2 * col] + red[(w * kRows + row) * 4 + 2 * col + 1];
+      }
+      if (col < p.M && n0 + row < p.N) {
+        if (p.nsplit == 1) {
+          p.y[static_cast<size_t>(col) * p.N + n0 + row] = __float2half_rn(v);
+        } else {
+          p.partials[(static_cast<size_t>(ks) * p.M + col) * p.N + n0 + row] = v;
+        }
+      }
+    }
+    if (p.nsplit > 1) {
+      __threadfence();
+      named_barrier(1, kConsumerThreads);
+      if (tid == 0) hdr->ticket = atomicAdd(&p.tickets[rt], 1);
+      named_barrier(1, kConsumerThreads);
+      if (hdr->ticket == p.nsplit - 1) {
+        __threadfence();
+        if (tid < 2 * kRows && col < p.M && n0 + row < p.N) {
+          float v = 0.0f;
+          for (int s = 0; s < p.nsplit; ++s) {
+            v += __ldcg(&p.partials[(static_cast<size_t>(s) * p.M + col) * p.N + n0 + row]);
+          }
+          p.y[static_cast<size_t>(col) * p.N + n0 + row] = __float2half_rn(v);
+        }
+        if (tid == 0) p.tickets[rt] = 0;
+      }
+    }
+    named_barrier(1, kConsumerThreads);
+  }
+}
+
+}  // namespace
+
+cudaError_t launch_gemv_decode(const Problem& p, const SkinnyPlan& plan, float* partials,
+                               int* tickets, int* status_word, bool pdl, cudaStream_t stream) {
+  DecodeParams kp;
+  kp.x = p.x;
+  kp.y = p.y;
+  kp.partials = partials;
+  kp.tickets = tickets;
+  kp.status = status_word;
+  kp.M = static_cast<int>(p.M);
+  kp.N = static_cast<int>(p.N);
+  kp.K = static_cast<int>(p.K);
+  kp.kseg = plan.kseg;
+  kp.nsplit = plan.nsplit;
+  kp.stage_k = plan.stage_k;
+  kp.stages_per_unit = plan.kseg / plan.stage_k;
+  kp.slots = plan.slots;
+  kp.row_tiles = plan.row_tiles;
+  kp.units = plan.row_tiles * plan.nsplit;
+  kp.packed_pitch = plan.packed_pitch;
+  kp.meta_pitch = plan.meta_pitch;
+  kp.slot_bytes = plan.slot_bytes;
+  kp.sx_offset = plan.sx_offset;
+  kp.red_offset = plan.red_offset;
+  kp.xf_offset = plan.xf_offset;
+  kp.ring_offset = plan.ring_offset;
+  CUtensorMap maps[3];
+  if (!skinny_encode_maps(p, plan, maps)) return cudaErrorInvalidValue;
+
+  // The opt-in to large dynamic shared memory is per device; repeating it is harmless.
+  static bool configured[64] = {};
+  int device = 0;
+  cudaError_t err = cudaGetDevice(&device);
+  if (err != cudaSuccess) return err;
+  if (device < 0 || device >= 64 || !configured[device]) {
+    err = cudaFuncSetAttribute(w4a16_gemv_decode_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                               216 * 1024);
+    if (err != cudaSuccess) return err;
+    if (device >= 0 && device < 64) configured[device] = true;
+  }
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3(static_cast<unsigned>(plan.grid));
+  cfg.blockDim = dim3(kThreads);
+  cfg.dynamicSmemBytes = static_cast<size_t>(plan.smem_bytes);
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = pdl ? 1 : 0;
+  return cudaLaunchKernelEx(&cfg, w4a16_gemv_decode_kernel, maps[0], maps[1], maps[2], kp);
+}
+
+}  // namespace lbl

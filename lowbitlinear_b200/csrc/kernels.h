@@ -6,6 +6,8 @@
 #include <stddef.h>
 #include <stdint.h>
 
+struct CUtensorMap_st;  // driver API tensor map (cuda.h)
+
 namespace lbl {
 
 // One W4A16 problem in the reference layout.  Pointers are device pointers.
@@ -30,6 +32,10 @@ struct SkinnyPlan {
   int grid;         // persistent CTAs
   int smem_bytes;   // dynamic shared memory per CTA
   int row_tiles;    // ceil(N / 16)
+  bool columns;     // M <= 2: the decode form (gemv_decode.cu) runs instead of the general one
+  int packed_pad;   // bytes of padding per packed row in shared memory
+  int packed_pitch, meta_pitch, slot_bytes;           // shared-memory layout of one ring slot
+  int sx_offset, red_offset, xf_offset, ring_offset;  // regions of the CTA's shared memory
   size_t partial_bytes;  // split-K partial sums (0 when nsplit == 1)
   size_t ticket_bytes;   // arrival counters (0 when nsplit == 1, else kSkinnyTicketBytes)
 };
@@ -48,6 +54,9 @@ bool skinny_supports(int64_t M, int64_t N, int64_t K);
 // > 0 asks for at least that many splits where the shape allows it.
 bool skinny_make_plan(int64_t M, int64_t N, int64_t K, int want_split, int sm_count,
                       SkinnyPlan* plan);
+bool skinny_encode_maps(const Problem& p, const SkinnyPlan& plan, ::CUtensorMap_st* maps);
+cudaError_t launch_gemv_decode(const Problem& p, const SkinnyPlan& plan, float* partials,
+                               int* tickets, int* status_word, bool pdl, cudaStream_t stream);
 cudaError_t launch_skinny(const Problem& p, const SkinnyPlan& plan, float* partials, int* tickets,
                           int* status_word, bool pdl, cudaStream_t stream);
 

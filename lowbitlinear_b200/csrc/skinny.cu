@@ -457,12 +457,17 @@ bool skinny_make_plan(int64_t M, int64_t N, int64_t K, int want_split, int sm_co
     }
   }
 
-  const int packed_pitch = stage_k / 2 + 32;
+  // The decode form (M <= 2) reads 16 bytes per lane and needs a row pitch of 64 mod 128 bytes;
+  // the general form reads 8 bytes per lane and needs 32 mod 128.
+  const bool columns = m <= 2 && env_int("LBL_GEMV_COLUMNS", 1) != 0;
+  const int packed_pad = columns ? 64 : 32;
+  const int packed_pitch = stage_k / 2 + packed_pad;
   const int meta_pitch = stage_k / 16 + 16;
   const int slot_bytes = kRows * packed_pitch + 2 * kRows * meta_pitch;
-  const int sx_bytes = (kseg / 64) * mc * 4;
-  const int red_bytes = kConsumerWarps * kRows * mc * 4;
-  const int xf_bytes = m * kseg * 2;
+  auto round128 = [](int v) { return (v + 127) / 128 * 128; };
+  const int sx_bytes = round128(columns ? (kseg / 64) * 2 * 4 : (kseg / 64) * mc * 4);
+  const int red_bytes = round128(columns ? kConsumerWarps * kRows * 4 * 4 : kConsumerWarps * kRows * mc * 4);
+  const int xf_bytes = round128(m * kseg * 2);
   const int fixed = kHeaderBytes + sx_bytes + red_bytes + xf_bytes;
 
   const int ctas_per_sm = std::max(1, std::min(2, env_int("LBL_SKINNY_CTAS_PER_SM", 2)));
@@ -484,16 +489,52 @@ bool skinny_make_plan(int64_t M, int64_t N, int64_t K, int want_split, int sm_co
   plan->grid = static_cast<int>(std::min<int64_t>(units, static_cast<int64_t>(per_sm) * sm_count));
   plan->smem_bytes = fixed + slots * slot_bytes;
   plan->row_tiles = row_tiles;
+  plan->columns = columns;
+  plan->packed_pad = packed_pad;
+  plan->packed_pitch = packed_pitch;
+  plan->meta_pitch = meta_pitch;
+  plan->slot_bytes = slot_bytes;
+  plan->sx_offset = kHeaderBytes;
+  plan->red_offset = plan->sx_offset + sx_bytes;
+  plan->xf_offset = plan->red_offset + red_bytes;
+  plan->ring_offset = plan->xf_offset + xf_bytes;
   plan->partial_bytes = nsplit > 1 ? static_cast<size_t>(nsplit) * M * N * sizeof(float) : 0;
   plan->ticket_bytes = nsplit > 1 ? kSkinnyTicketBytes : 0;
   return units <= 0x7fffffffLL;
 }
 
+// Tensor maps over the reference layout.  Each row is viewed as [K / stage_k][stage_k]; a box
+// takes 16 rows of one stage plus a few elements of padding per row.  The padding is outside the
+// inner extent, so it is zero-filled and costs no traffic, and it gives the rows in shared memory
+// the pitch that keeps the fragment loads free of bank conflicts.
+bool skinny_encode_maps(const Problem& p, const SkinnyPlan& plan, CUtensorMap* maps) {
+  const uint64_t stages_in_row = static_cast<uint64_t>(p.K / plan.stage_k);
+  const uint64_t n_rows = static_cast<uint64_t>(p.N);
+  {
+    const uint64_t dims[3] = {static_cast<uint64_t>(plan.stage_k / 16), stages_in_row, n_rows};
+    const uint64_t strides[2] = {static_cast<uint64_t>(plan.stage_k / 2),
+                                 static_cast<uint64_t>(p.K / 2)};
+    const uint32_t box[3] = {static_cast<uint32_t>(plan.stage_k / 16 + plan.packed_pad / 8), 1, kRows};
+    if (!encode_tensor_map(&maps[0], CU_TENSOR_MAP_DATA_TYPE_UINT64, 3, p.packed, dims, strides, box,
+                           CU_TENSOR_MAP_SWIZZLE_NONE)) {
+      return false;
+    }
+  }
+  const uint64_t dims[3] = {static_cast<uint64_t>(plan.stage_k / 64), stages_in_row, n_rows};
+  const uint64_t strides[2] = {static_cast<uint64_t>(plan.stage_k / 16),
+                               static_cast<uint64_t>(p.K / 16)};
+  const uint32_t box[3] = {static_cast<uint32_t>(plan.stage_k / 64 + 4), 1, kRows};
+  return encode_tensor_map(&maps[1], CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 3, p.scales, dims, strides, box,
+                           CU_TENSOR_MAP_SWIZZLE_NONE) &&
+         encode_tensor_map(&maps[2], CU_TENSOR_MAP_DATA_TYPE_INT32, 3, p.zeros, dims, strides, box,
+                           CU_TENSOR_MAP_SWIZZLE_NONE);
+}
+
 cudaError_t launch_skinny(const Problem& p, const SkinnyPlan& plan, float* partials, int* tickets,
                           int* status_word, bool pdl, cudaStream_t stream) {
+  if (plan.columns) return launch_gemv_decode(p, plan, partials, tickets, status_word, pdl, stream);
   const int m = static_cast<int>(p.M);
   const int nt = m <= 8 ? 1 : (m <= 16 ? 2 : 4);
-  const int mc = 8 * nt;
   KernelParams kp;
   kp.x = p.x;
   kp.y = p.y;
@@ -510,43 +551,15 @@ cudaError_t launch_skinny(const Problem& p, const SkinnyPlan& plan, float* parti
   kp.slots = plan.slots;
   kp.row_tiles = plan.row_tiles;
   kp.units = plan.row_tiles * plan.nsplit;
-  kp.packed_pitch = plan.stage_k / 2 + 32;
-  kp.meta_pitch = plan.stage_k / 16 + 16;
-  kp.slot_bytes = kRows * kp.packed_pitch + 2 * kRows * kp.meta_pitch;
-  kp.sx_offset = kHeaderBytes;
-  kp.red_offset = kp.sx_offset + (plan.kseg / 64) * mc * 4;
-  kp.xf_offset = kp.red_offset + kConsumerWarps * kRows * mc * 4;
-  kp.ring_offset = kp.xf_offset + m * plan.kseg * 2;
-  // Tensor maps over the reference layout.  Each row is viewed as [K / stage_k][stage_k]; a box
-  // takes 16 rows of one stage plus 4 elements of padding per row.  The padding is outside the
-  // inner extent, so it is zero-filled and costs no traffic, and it gives the rows in shared
-  // memory the pitch (stage bytes + 32 resp. + 16) that keeps the fragment loads free of
-  // bank conflicts.
+  kp.packed_pitch = plan.packed_pitch;
+  kp.meta_pitch = plan.meta_pitch;
+  kp.slot_bytes = plan.slot_bytes;
+  kp.sx_offset = plan.sx_offset;
+  kp.red_offset = plan.red_offset;
+  kp.xf_offset = plan.xf_offset;
+  kp.ring_offset = plan.ring_offset;
   CUtensorMap maps[3];
-  const uint64_t stages_in_row = static_cast<uint64_t>(p.K / plan.stage_k);
-  const uint64_t n_rows = static_cast<uint64_t>(p.N);
-  {
-    const uint64_t dims[3] = {static_cast<uint64_t>(plan.stage_k / 16), stages_in_row, n_rows};
-    const uint64_t strides[2] = {static_cast<uint64_t>(plan.stage_k / 2),
-                                 static_cast<uint64_t>(p.K / 2)};
-    const uint32_t box[3] = {static_cast<uint32_t>(plan.stage_k / 16 + 4), 1, kRows};
-    if (!encode_tensor_map(&maps[0], CU_TENSOR_MAP_DATA_TYPE_UINT64, 3, p.packed, dims, strides, box,
-                           CU_TENSOR_MAP_SWIZZLE_NONE)) {
-      return cudaErrorInvalidValue;
-    }
-  }
-  {
-    const uint64_t dims[3] = {static_cast<uint64_t>(plan.stage_k / 64), stages_in_row, n_rows};
-    const uint64_t strides[2] = {static_cast<uint64_t>(plan.stage_k / 16),
-                                 static_cast<uint64_t>(p.K / 16)};
-    const uint32_t box[3] = {static_cast<uint32_t>(plan.stage_k / 64 + 4), 1, kRows};
-    if (!encode_tensor_map(&maps[1], CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 3, p.scales, dims, strides, box,
-                           CU_TENSOR_MAP_SWIZZLE_NONE) ||
-        !encode_tensor_map(&maps[2], CU_TENSOR_MAP_DATA_TYPE_INT32, 3, p.zeros, dims, strides, box,
-                           CU_TENSOR_MAP_SWIZZLE_NONE)) {
-      return cudaErrorInvalidValue;
-    }
-  }
+  if (!skinny_encode_maps(p, plan, maps)) return cudaErrorInvalidValue;
   switch (nt) {
     case 1:
       return launch_nt<1>(maps, kp, plan, pdl, stream);
