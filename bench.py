@@ -452,14 +452,22 @@ def run_ours(args):
     amount = per_layer * LAYERS  # whole job, all ranks together
     value = amount / (ms_per_step * 1e-3)
     launches_per_step = len(layers)
+    # DRAM bytes per launch: ratio of (dram read + write) to algorithmic bytes from the committed
+    # ncu captures of one Gate/Up launch (profiles/), applied to this rank's average launch;
+    # traffic follows the weights in proportion, there are no re-reads.
+    algorithmic_bytes_per_launch = sum(linear_bytes(m, SHAPES[i][1], SHAPES[i][2]) for i in all_idx) / 4.0 / world
+    traffic_ratio = 1.004 if args.workload == "decode" else 0.767
+    traffic = traffic_ratio * algorithmic_bytes_per_launch
     if args.workload == "decode":
         roofline = {"bound": "hbm", "achieved": value / world, "peak": peaks["hbm_gbs"], "unit": "GB/s",
-                    "frac": value / world / peaks["hbm_gbs"], "traffic": None,
-                    "kernel": "w4a16_skinny_kernel", "peak_source": peaks["source"],
+                    "frac": value / world / peaks["hbm_gbs"], "traffic": traffic,
+                    "traffic_unit": "bytes per launch (ncu dram read+write of one Gate/Up launch, scaled)",
+                    "kernel": "w4a16_gemv_decode_kernel", "peak_source": peaks["source"],
                     "per_launch": "per-GPU algorithmic bytes of the step / 144 launches, over the step's CUDA-event time / 144"}
     else:
         roofline = {"bound": "tensor", "achieved": value / world, "peak": peaks["tflops_sustained"], "unit": "TFLOP/s",
-                    "frac": value / world / peaks["tflops_sustained"], "traffic": None,
+                    "frac": value / world / peaks["tflops_sustained"], "traffic": traffic,
+                    "traffic_unit": "bytes per launch (ncu dram read+write of one Gate/Up launch, scaled)",
                     "kernel": "w4a16_gemm_tc_kernel", "peak_source": peaks["source"] + " (sustained bf16)",
                     "per_launch": "per-GPU flops of the step / 144 launches, over the step's CUDA-event time / 144"}
     if rank != 0:

@@ -48,6 +48,8 @@ struct Header {
   uint64_t empty[kMaxSlots];
   int abort_flag;
   int ticket;
+  int pad[14];
+  uint4 zeros[4];  // B operand of the lanes that feed no activation column
 };
 static_assert(sizeof(Header) <= kHeaderBytes, "header does not fit");
 
@@ -119,6 +121,7 @@ __global__ void __launch_bounds__(kThreads, 2)
     }
     hdr->abort_flag = 0;
     hdr->ticket = 0;
+    for (int i = 0; i < 4; ++i) hdr->zeros[i] = make_uint4(0u, 0u, 0u, 0u);
     mbar_init_fence();
   }
   __syncthreads();
@@ -202,7 +205,10 @@ __global__ void __launch_bounds__(kThreads, 2)
       const float* sc_b = reinterpret_cast<const float*>(base + scales_block + (g + 8) * p.meta_pitch) + group_parity;
       const int* zp_a = reinterpret_cast<const int*>(base + zeros_block + g * p.meta_pitch) + group_parity;
       const int* zp_b = reinterpret_cast<const int*>(base + zeros_block + (g + 8) * p.meta_pitch) + group_parity;
-      const uint4* xf_lane = xf + feed_row * words_seg + st * (p.stage_k / 8) + t * 4;
+      // Lanes without an activation column read the block of zeros, with stride 0.
+      const uint4* xf_lane =
+          feeds_b ? xf + feed_row * words_seg + st * (p.stage_k / 8) + t * 4 : hdr->zeros;
+      const int xf_stride = feeds_b ? 16 : 0;
       const float* sx_lane = sx + (st * (p.stage_k / 64) + group_parity) * 2 + out_row;
 
 #pragma unroll 2
@@ -211,11 +217,7 @@ __global__ void __launch_bounds__(kThreads, 2)
         const uint4 wb = *reinterpret_cast<const uint4*>(row_b + j * 64);
         uint4 xb[4];
 #pragma unroll
-        for (int i = 0; i < 4; ++i) xb[i] = make_uint4(0u, 0u, 0u, 0u);
-        if (feeds_b) {
-#pragma unroll
-          for (int i = 0; i < 4; ++i) xb[i] = xf_lane[j * 16 + i];
-        }
+        for (int i = 0; i < 4; ++i) xb[i] = xf_lane[j * xf_stride + i];
         const float scale_a = sc_a[2 * j];
         const float scale_b = sc_b[2 * j];
         const float zero_a = static_cast<float>(zp_a[2 * j]);
