@@ -97,6 +97,30 @@ int lbl_w4a16_linear(const void* X, const int32_t* packed_w, const float* scales
                      int path, void* workspace, size_t workspace_bytes, unsigned flags,
                      int device, void* stream, int* path_taken);
 
+/* The M = 1 GEMV for callers that have no way to allocate device memory: a plugin that is
+ * handed nothing but input and output pointers by its host application, code that runs where
+ * cudaMalloc is not allowed (it synchronises the whole device, and is illegal while a stream
+ * is being captured), or a process whose memory budget was fixed up front.  (No counterpart in
+ * the reference; its launchers allocate through torch.)
+ *
+ * It is lbl_w4a16_gemv with K split across CTAs, but the split-K scratch (arrival counters and
+ * FP32 partial sums) is a fixed array of lbl_w4a16_gemv_noalloc_scratch_bytes() = 1 MiB inside
+ * the library image: every GPU that loads the library holds that megabyte until the process
+ * ends, and the call itself performs no cudaMalloc, cudaFree or any other allocation.
+ *  - Limit: 64 KiB + nsplit * N * 4 bytes must fit (for example N = 4096 with K = 12288, or
+ *    N = 24576 with K = 4096).  Larger problems are rejected with LBL_ERR_WORKSPACE and a
+ *    message; use lbl_w4a16_gemv with your own workspace for those.
+ *  - The first call on each device looks up the array's device address and clears its counters
+ *    on `stream`; make that first call outside any stream capture.
+ *  - All calls on a device share the one array, which keeps what the last call left in it (the
+ *    kernel puts its counters back to zero before it ends).  Two calls that overlap on the GPU,
+ *    for instance from different streams, race on it; serialise them.
+ * Same argument contract as lbl_w4a16_gemv otherwise (K % 256 == 0, 16-byte aligned tensors). */
+size_t lbl_w4a16_gemv_noalloc_scratch_bytes(void);
+int lbl_w4a16_gemv_noalloc(const void* x, const int32_t* packed_w, const float* scales,
+                           const int32_t* zeros, void* y, int64_t N, int64_t K, int group_size,
+                           unsigned flags, int device, void* stream);
+
 /* Reads (and clears) the device-side status word of `device`: 0, or a code left by a
  * kernel whose bounded wait on a barrier expired.  Synchronises the device. */
 int lbl_device_status(int device, int* status);

@@ -311,4 +311,95 @@ int lbl_device_status(int device, int* status) {
   return LBL_OK;
 }
 
+// ---------------------------------------------------------------------------------------------
+// GEMV for callers that cannot allocate device memory.
+//
+// Split-K needs scratch (arrival counters and FP32 partial sums).  Here it lives in a fixed
+// array that is part of the library image, so the caller provides inputs and outputs only.
+// Every GPU that loads the library carries these bytes until the process exits.
+// ---------------------------------------------------------------------------------------------
+}  // extern "C"
+
+namespace {
+
+constexpr size_t kStaticScratchBytes = 1u << 20;  // 64 KiB of counters + 960 KiB of partial sums
+static __device__ __align__(256) unsigned char g_static_scratch[kStaticScratchBytes];
+
+// In host code `g_static_scratch` is only a handle for the runtime; the device address has to be
+// asked for, once per device and with that device current.
+void* g_static_scratch_address[kMaxDevices] = {};
+std::mutex g_static_scratch_mutex;
+
+// Requires `device` to be current.  The first call per device also clears the counters.
+int static_scratch(int device, cudaStream_t stream, void** out) {
+  std::lock_guard<std::mutex> lock(g_static_scratch_mutex);
+  if (g_static_scratch_address[device] == nullptr) {
+    void* ptr = nullptr;
+    cudaError_t err = cudaGetSymbolAddress(&ptr, g_static_scratch);
+    if (err != cudaSuccess) return fail_cuda(err, "cudaGetSymbolAddress(static scratch)");
+    err = cudaMemsetAsync(ptr, 0, lbl::kSkinnyTicketBytes, stream);
+    if (err != cudaSuccess) return fail_cuda(err, "cudaMemsetAsync(static scratch)");
+    g_static_scratch_address[device] = ptr;
+  }
+  *out = g_static_scratch_address[device];
+  return LBL_OK;
+}
+
+}  // namespace
+
+extern "C" {
+
+size_t lbl_w4a16_gemv_noalloc_scratch_bytes(void) { return kStaticScratchBytes; }
+
+int lbl_w4a16_gemv_noalloc(const void* x, const int32_t* packed_w, const float* scales,
+                           const int32_t* zeros, void* y, int64_t N, int64_t K, int group_size,
+                           unsigned flags, int device, void* stream) {
+  if (group_size != 64 || K <= 0 || K % 64 != 0) {
+    return fail(LBL_ERR_INVALID, "Expected group_size=64 and K divisible by 64 (group_size=%d K=%lld)", group_size, (long long)K);
+  }
+  if (N <= 0 || N > 0x7fffffffLL || K > 0x7fffffffLL) return fail(LBL_ERR_INVALID, "Invalid N or K");
+  if (x == nullptr || packed_w == nullptr || scales == nullptr || zeros == nullptr || y == nullptr) {
+    return fail(LBL_ERR_INVALID, "null tensor pointer");
+  }
+  if (!aligned16(x) || !aligned16(packed_w) || !aligned16(scales) || !aligned16(zeros) || !aligned16(y)) {
+    return fail(LBL_ERR_INVALID, "all tensors must be 16-byte aligned");
+  }
+  cudaStream_t cu_stream = static_cast<cudaStream_t>(stream);
+  DeviceScope scope(device);
+  if (!scope.ok()) return fail(LBL_ERR_CUDA, "cannot make device %d current", device);
+  DeviceInfo info;
+  int rc = device_info(device, &info);
+  if (rc != LBL_OK) return rc;
+
+  lbl::SkinnyPlan plan;
+  if (!lbl::skinny_make_plan(1, N, K, /*want_split=*/2, info.sm_count, &plan)) {
+    return fail(LBL_ERR_UNSUPPORTED, "the streaming kernel needs K %% 256 == 0 (K=%lld)", (long long)K);
+  }
+  const size_t need = plan.partial_bytes + plan.ticket_bytes;
+  if (need > kStaticScratchBytes) {
+    return fail(LBL_ERR_WORKSPACE, "N=%lld K=%lld needs %zu bytes of split-K scratch; the built-in scratch holds %zu. Use lbl_w4a16_gemv with a caller-provided workspace", (long long)N, (long long)K, need, kStaticScratchBytes);
+  }
+  void* scratch = nullptr;
+  rc = static_scratch(device, cu_stream, &scratch);
+  if (rc != LBL_OK) return rc;
+
+  lbl::Problem prob;
+  prob.x = static_cast<const __half*>(x);
+  prob.packed = reinterpret_cast<const uint32_t*>(packed_w);
+  prob.scales = scales;
+  prob.zeros = zeros;
+  prob.y = static_cast<__half*>(y);
+  prob.M = 1;
+  prob.N = N;
+  prob.K = K;
+  int* tickets = plan.nsplit > 1 ? static_cast<int*>(scratch) : nullptr;
+  float* partials = plan.nsplit > 1
+                        ? reinterpret_cast<float*>(static_cast<char*>(scratch) + plan.ticket_bytes)
+                        : nullptr;
+  const cudaError_t err = lbl::launch_skinny(prob, plan, partials, tickets, info.status_word,
+                                             (flags & LBL_FLAG_PDL) != 0, cu_stream);
+  if (err != cudaSuccess) return fail_cuda(err, "kernel launch");
+  return LBL_OK;
+}
+
 }  // extern "C"
