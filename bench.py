@@ -276,6 +276,28 @@ def check_parity(actual, expected, what):
     return rel
 
 
+def note(message):
+    """Progress line on stderr (only with BENCH_VERBOSE=1): shows where a multi-rank run is."""
+    if os.environ.get("BENCH_VERBOSE"):
+        print(f"[bench rank {os.environ.get('RANK', '0')} {time.strftime('%H:%M:%S')}] {message}",
+              file=sys.stderr, flush=True)
+
+
+def leave_process_group(world):
+    """End a multi-rank run.  Tearing down an NCCL communicator whose collectives live in a
+    captured CUDA graph can block for minutes, so the ranks meet at a barrier, flush their
+    output and leave without running the destructors."""
+    if world <= 1:
+        return
+    import torch.distributed as dist
+
+    torch.cuda.synchronize()
+    dist.barrier()
+    sys.stdout.flush()
+    sys.stderr.flush()
+    os._exit(0)
+
+
 def run_ours(args):
     import torch.distributed as dist
 
@@ -287,7 +309,8 @@ def run_ours(args):
     torch.cuda.set_device(local_rank)
     device = torch.device("cuda", local_rank)
     if world > 1:
-        dist.init_process_group("nccl", device_id=device)
+        import datetime
+        dist.init_process_group("nccl", timeout=datetime.timedelta(seconds=180))
     if world != args.gpus:
         raise SystemExit(f"--gpus {args.gpus} but WORLD_SIZE={world}; launch with torchrun for N > 1")
 
@@ -312,11 +335,13 @@ def run_ours(args):
             host_layer0 = [host_layer0_map[i] for i in range(4)]
 
     with torch.inference_mode():
+        note("building the stack")
         layers, xs = build_stack(m, device, rank, world, host_layer0)
         torch.cuda.synchronize()
 
         # ---- correctness before timing -----------------------------------------------------------
         _ops.set_programmatic_dependent_launch(False)
+        note("eager pass")
         eager = run_stack(layers, xs, world)
         torch.cuda.synchronize()
         parity = {}
@@ -344,7 +369,12 @@ def run_ours(args):
                 del q, w
 
         # ---- capture one step as a CUDA graph ---------------------------------------------------
-        _ops.set_programmatic_dependent_launch(bool(args.pdl))
+        note("capturing the step")
+        # Between tensor-parallel ranks the kernels alternate with NCCL kernels; a dependent
+        # launch that holds SM resources while it waits for a collective could starve it, so
+        # programmatic dependent launch is used on a single GPU only.
+        use_pdl = bool(args.pdl) and world == 1
+        _ops.set_programmatic_dependent_launch(use_pdl)
         side = torch.cuda.Stream()
         side.wait_stream(torch.cuda.current_stream())
         with torch.cuda.stream(side):
@@ -355,6 +385,7 @@ def run_ours(args):
         graph = torch.cuda.CUDAGraph()
         with torch.cuda.graph(graph, stream=side):
             graph_out = run_stack(layers, xs, world)
+        note("first replay")
         graph.replay()
         torch.cuda.synchronize()
         for i, (a, b) in enumerate(zip(graph_out, eager)):
@@ -362,6 +393,8 @@ def run_ours(args):
                 if world > 1 and layers[i][0] == "down":
                     continue  # all-reduce order may differ between eager and captured runs
                 raise SystemExit(f"graph replay differs from eager run on linear {i}")
+
+        note("timed region")
 
         def barrier():
             if world > 1:
@@ -383,22 +416,23 @@ def run_ours(args):
         barrier()
         t1 = time.perf_counter()
         elapsed_ms = start.elapsed_time(end)
-        if rank == 0 and t1 - t0 < 1.5:
-            # The timed region was too short for nvidia-smi to sample: hold the same load a
-            # little longer for the clock record only.
-            hold_until = time.perf_counter() + 1.5
-            while time.perf_counter() < hold_until:
-                for _ in range(20):
-                    graph.replay()
-                torch.cuda.synchronize()
-            t1 = time.perf_counter()
-        clocks = sampler.stop(t0, t1) if sampler is not None else None
         if world > 1:
             t = torch.tensor([elapsed_ms], device=device)
             dist.all_reduce(t, op=dist.ReduceOp.MAX)
             elapsed_ms = t.item()
+        if elapsed_ms < 1500.0:
+            # The timed region was too short for nvidia-smi to sample: hold the same load a
+            # little longer, for the clock record only.  Every rank replays the same number of
+            # times (the count derives from the reduced time), since the graph holds collectives.
+            hold_replays = int(1500.0 / max(elapsed_ms / args.steps, 1e-3)) + 1
+            for _ in range(hold_replays):
+                graph.replay()
+            torch.cuda.synchronize()
+            t1 = time.perf_counter()
+        clocks = sampler.stop(t0, t1) if sampler is not None else None
         ms_per_step = elapsed_ms / args.steps
 
+        note("end-to-end region")
         # ---- end to end through the public API, host buffers ---------------------------------------
         _ops.set_programmatic_dependent_launch(False)
         # Decode: the whole stack's activations go up in one pinned copy and all outputs come
@@ -471,15 +505,14 @@ def run_ours(args):
                     "kernel": "w4a16_gemm_tc_kernel", "peak_source": peaks["source"] + " (sustained bf16)",
                     "per_launch": "per-GPU flops of the step / 144 launches, over the step's CUDA-event time / 144"}
     if rank != 0:
-        if world > 1:
-            dist.destroy_process_group()
+        leave_process_group(world)
         return
     line = {
         "metric": metric_name(args.workload), "value": value, "unit": unit, "n_gpus": world,
         "steps": args.steps, "warmup": max(args.warmup, 3), "ms_per_step": ms_per_step,
         "higher_is_better": True, "scaling": "strong", "vs_baseline": None,
         "dtype": "f16 activations x int4 weights, f32 accumulate", "data": "synthetic",
-        "config": config_of(args.workload, m, world, args.pdl),
+        "config": config_of(args.workload, m, world, args.pdl and world == 1),
         "roofline": roofline, "cpu_baseline": cpu_baseline, "clocks": clocks,
         "e2e": {"value": amount / (e2e_ms * 1e-3), "unit": unit, "ms_per_step": e2e_ms,
                 "h2d_bytes_per_step": int(host_x.numel() * 2 * chunks_per_step),
@@ -490,8 +523,7 @@ def run_ours(args):
         "fraction_of_nominal": value / world / (8000.0 if args.workload == "decode" else 2250.0),
     }
     print(json.dumps(line), flush=True)
-    if world > 1:
-        dist.destroy_process_group()
+    leave_process_group(world)
 
 
 def main():
