@@ -53,6 +53,25 @@ struct Header {
 };
 static_assert(sizeof(Header) <= kHeaderBytes, "header does not fit");
 
+// Shared-memory loads by 32-bit address (volatile: they stay behind the barrier wait).
+__device__ __forceinline__ uint4 lds128(uint32_t addr) {
+  uint4 v;
+  asm volatile("ld.shared.v4.u32 {%0, %1, %2, %3}, [%4];"
+               : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w)
+               : "r"(addr));
+  return v;
+}
+__device__ __forceinline__ float lds_f32(uint32_t addr) {
+  float v;
+  asm volatile("ld.shared.f32 %0, [%1];" : "=f"(v) : "r"(addr));
+  return v;
+}
+__device__ __forceinline__ int lds_s32(uint32_t addr) {
+  int v;
+  asm volatile("ld.shared.s32 %0, [%1];" : "=r"(v) : "r"(addr));
+  return v;
+}
+
 __device__ __forceinline__ uint32_t pack_half2(__half lo, __half hi) {
   return static_cast<uint32_t>(__half_as_ushort(lo)) |
          (static_cast<uint32_t>(__half_as_ushort(hi)) << 16);
@@ -175,6 +194,13 @@ __global__ void __launch_bounds__(kThreads, 2)
   const int macro_per_stage = p.stage_k / 128;
   const int words_seg = p.kseg / 8;
   const float zero4[4] = {0.0f, 0.0f, 0.0f, 0.0f};
+  const uint32_t ring_addr = smem_addr(ring);
+  const uint32_t sx_base = smem_addr(sx) + static_cast<uint32_t>(group_parity * 2 + out_row) * 4;
+  const uint32_t xf_addr = smem_addr(xf) + static_cast<uint32_t>(feed_row * words_seg + t * 4) * 16;
+  // Lanes that feed no activation column never load: their B registers stay zero for good.
+  uint4 xb[4];
+#pragma unroll
+  for (int i = 0; i < 4; ++i) xb[i] = make_uint4(0u, 0u, 0u, 0u);
 
   int it = 0;
   int current_ks = -1;
@@ -198,31 +224,29 @@ __global__ void __launch_bounds__(kThreads, 2)
       const int round = it / p.slots;
       mbar_wait_bounded(&hdr->full[slot], round & 1, abort_flag, p.status, kStatusSkinnyFullWait);
 
-      const uint8_t* base = ring + static_cast<size_t>(slot) * p.slot_bytes;
-      const uint8_t* row_a = base + g * p.packed_pitch + t * 16;
-      const uint8_t* row_b = row_a + 8 * p.packed_pitch;
-      const float* sc_a = reinterpret_cast<const float*>(base + scales_block + g * p.meta_pitch) + group_parity;
-      const float* sc_b = reinterpret_cast<const float*>(base + scales_block + (g + 8) * p.meta_pitch) + group_parity;
-      const int* zp_a = reinterpret_cast<const int*>(base + zeros_block + g * p.meta_pitch) + group_parity;
-      const int* zp_b = reinterpret_cast<const int*>(base + zeros_block + (g + 8) * p.meta_pitch) + group_parity;
-      // Lanes without an activation column read the block of zeros, with stride 0.
-      const uint4* xf_lane =
-          feeds_b ? xf + feed_row * words_seg + st * (p.stage_k / 8) + t * 4 : hdr->zeros;
-      const int xf_stride = feeds_b ? 16 : 0;
-      const float* sx_lane = sx + (st * (p.stage_k / 64) + group_parity) * 2 + out_row;
+      // 32-bit shared-memory addresses of this lane's operands for macro tile `warp`; macro tile
+      // warp + 8 u lies at a fixed distance from it.
+      const uint32_t base = ring_addr + static_cast<uint32_t>(slot * p.slot_bytes);
+      const uint32_t wa_addr = base + g * p.packed_pitch + t * 16 + warp * 64;
+      const uint32_t wb_addr = wa_addr + 8 * p.packed_pitch;
+      const uint32_t meta_a = base + scales_block + g * p.meta_pitch + (2 * warp + group_parity) * 4;
+      const uint32_t meta_b = meta_a + 8 * p.meta_pitch;
+      const uint32_t zero_delta = static_cast<uint32_t>(kRows * p.meta_pitch);  // scales -> zero points
+      const uint32_t xb_addr = xf_addr + static_cast<uint32_t>(st * (p.stage_k / 8) + warp * 16) * 16;
+      const uint32_t sx_addr = sx_base + static_cast<uint32_t>(st * (p.stage_k / 64) + 2 * warp) * 8;
 
-#pragma unroll 2
-      for (int j = warp; j < macro_per_stage; j += kConsumerWarps) {
-        const uint4 wa = *reinterpret_cast<const uint4*>(row_a + j * 64);
-        const uint4 wb = *reinterpret_cast<const uint4*>(row_b + j * 64);
-        uint4 xb[4];
+      auto macro_tile = [&](int u) {
+        const uint4 wa = lds128(wa_addr + u * 512);
+        const uint4 wb = lds128(wb_addr + u * 512);
+        if (feeds_b) {
 #pragma unroll
-        for (int i = 0; i < 4; ++i) xb[i] = xf_lane[j * xf_stride + i];
-        const float scale_a = sc_a[2 * j];
-        const float scale_b = sc_b[2 * j];
-        const float zero_a = static_cast<float>(zp_a[2 * j]);
-        const float zero_b = static_cast<float>(zp_b[2 * j]);
-        const float sum_x = sx_lane[4 * j];
+          for (int i = 0; i < 4; ++i) xb[i] = lds128(xb_addr + u * 2048 + i * 16);
+        }
+        const float scale_a = lds_f32(meta_a + u * 64);
+        const float scale_b = lds_f32(meta_b + u * 64);
+        const float zero_a = static_cast<float>(lds_s32(meta_a + zero_delta + u * 64));
+        const float zero_b = static_cast<float>(lds_s32(meta_b + zero_delta + u * 64));
+        const float sum_x = lds_f32(sx_addr + u * 128);
 
         const uint32_t words_a[4] = {wa.x, wa.y, wa.z, wa.w};
         const uint32_t words_b[4] = {wb.x, wb.y, wb.z, wb.w};
@@ -250,6 +274,14 @@ __global__ void __launch_bounds__(kThreads, 2)
         acc_b = fmaf(scale_b * kNibbleUnit, qx_b, acc_b);
         acc_a = fmaf(-(scale_a * zero_a), sum_x, acc_a);
         acc_b = fmaf(-(scale_b * zero_b), sum_x, acc_b);
+      };
+      if (macro_per_stage == 16) {  // stage of 2048 columns: two macro tiles per warp
+        macro_tile(0);
+        macro_tile(1);
+      } else if (macro_per_stage == 8) {
+        macro_tile(0);
+      } else {
+        for (int u = 0; warp + 8 * u < macro_per_stage; ++u) macro_tile(u);
       }
       __syncwarp();
       if (lane == 0) mbar_arrive(&hdr->empty[slot]);
