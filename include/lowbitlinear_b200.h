@@ -121,6 +121,29 @@ int lbl_w4a16_gemv_noalloc(const void* x, const int32_t* packed_w, const float* 
                            const int32_t* zeros, void* y, int64_t N, int64_t K, int group_size,
                            unsigned flags, int device, void* stream);
 
+/* ---- Row-parallel (K-split) GEMV with the all-reduce fused into the kernel -----------------
+ * The reference has no multi-GPU code; this is the tensor-parallel form of its Down projection.
+ * Every rank (one process per GPU, same node) owns an exchange buffer created with
+ * lbl_peer_buffer_create, exports its 64-byte IPC handle, and opens the handles of its peers.
+ * lbl_w4a16_gemv_allreduce computes this rank's partial y over its K slice, leaves the FP32
+ * vector in its own buffer, raises a flag in every peer's buffer, waits (bounded, about 2 s)
+ * for the peers' flags, and adds the ranks' vectors in rank order over NVLink peer loads:
+ * every rank ends with the same FP16 y[1, N].  All ranks must make the same sequence of calls.
+ * buffers[r] is rank r's buffer as mapped in this process (buffers[rank] = own buffer),
+ * buffer_capacity_n the max_n all buffers were sized for.  Buffers are double-buffered by
+ * call parity, so calls may follow each other without a host synchronisation. */
+size_t lbl_peer_buffer_bytes(int64_t max_n);
+int lbl_peer_buffer_create(size_t bytes, int device, void** buffer);
+int lbl_peer_buffer_export(const void* buffer, void* handle64);
+int lbl_peer_buffer_open(const void* handle64, int device, void** buffer);
+int lbl_peer_buffer_close(void* buffer, int device);
+int lbl_peer_buffer_destroy(void* buffer, int device);
+int lbl_w4a16_gemv_allreduce(const void* x, const int32_t* packed_w, const float* scales,
+                             const int32_t* zeros, void* y, int64_t N, int64_t K, int group_size,
+                             int rank, int world, void* const* buffers, int64_t buffer_capacity_n,
+                             void* workspace, size_t workspace_bytes, unsigned flags, int device,
+                             void* stream);
+
 /* Reads (and clears) the device-side status word of `device`: 0, or a code left by a
  * kernel whose bounded wait on a barrier expired.  Synchronises the device. */
 int lbl_device_status(int device, int* status);

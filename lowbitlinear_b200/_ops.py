@@ -63,6 +63,21 @@ def bind(path):
                                      ctypes.POINTER(ctypes.c_int)]
     lib.lbl_device_status.restype = i32
     lib.lbl_device_status.argtypes = [i32, ctypes.POINTER(ctypes.c_int)]
+    lib.lbl_peer_buffer_bytes.restype = sz
+    lib.lbl_peer_buffer_bytes.argtypes = [i64]
+    lib.lbl_peer_buffer_create.restype = i32
+    lib.lbl_peer_buffer_create.argtypes = [sz, i32, ctypes.POINTER(p)]
+    lib.lbl_peer_buffer_export.restype = i32
+    lib.lbl_peer_buffer_export.argtypes = [p, p]
+    lib.lbl_peer_buffer_open.restype = i32
+    lib.lbl_peer_buffer_open.argtypes = [p, i32, ctypes.POINTER(p)]
+    lib.lbl_peer_buffer_close.restype = i32
+    lib.lbl_peer_buffer_close.argtypes = [p, i32]
+    lib.lbl_peer_buffer_destroy.restype = i32
+    lib.lbl_peer_buffer_destroy.argtypes = [p, i32]
+    lib.lbl_w4a16_gemv_allreduce.restype = i32
+    lib.lbl_w4a16_gemv_allreduce.argtypes = [p, p, p, p, p, i64, i64, i32, i32, i32, ctypes.POINTER(p), i64,
+                                             p, sz, u32, i32, p]
     _lib = lib
     return lib
 
@@ -207,6 +222,21 @@ def linear_forced(X, packed_w, scales, zeros, path, op=1, flags=None):
                                  _flags if flags is None else flags, X.device.index, stream,
                                  ctypes.byref(taken)))
     return Y, taken.value
+
+
+def gemv_allreduce(x, packed_w, scales, zeros, exchange):
+    """K-split GEMV with the all-reduce fused into the kernel: ``x`` is this rank's ``[1, K/g]``
+    slice, the weights its column slice; returns the full ``[1, N]`` (identical on every rank).
+    ``exchange`` is a ``tensor_parallel.PeerExchange``."""
+    n, k = packed_w.size(0), x.size(1)
+    y = torch.empty((1, n), dtype=torch.float16, device=x.device)
+    stream = torch.cuda.current_stream(x.device).cuda_stream
+    ws, ws_bytes = _workspace(x.device, stream, 1, n, k)
+    _check(_lib.lbl_w4a16_gemv_allreduce(x.data_ptr(), packed_w.data_ptr(), scales.data_ptr(),
+                                         zeros.data_ptr(), y.data_ptr(), n, k, 64, exchange.rank,
+                                         exchange.world, exchange.pointers, exchange.capacity_n, ws,
+                                         ws_bytes, _flags, x.device.index, stream))
+    return y
 
 
 def select_path(m, n, k, op=1):

@@ -7,6 +7,7 @@
 #include <cstdarg>
 #include <cstdio>
 #include <cstdlib>
+#include <cstring>
 #include <mutex>
 
 namespace {
@@ -104,7 +105,10 @@ int select_path(int64_t M, int64_t N, int64_t K, int op, int sm_count) {
   if (M <= 0 || N <= 0 || K <= 0) return LBL_PATH_GENERIC;
   const bool skinny_ok = lbl::skinny_supports(M, N, K);
   const bool tc_ok = lbl::gemm_tc_supports(M, N, K);
-  if (tc_ok && (M >= tc_min_m() || !skinny_ok)) return LBL_PATH_GEMM_TC;
+  // Measured crossover (B200): the streaming kernels win up to M = 16; from M = 9 the
+  // tensor-core GEMM already wins when N is large enough to fill the SMs with 256-wide tiles.
+  const bool wide = N >= 16384;
+  if (tc_ok && (M >= tc_min_m() || (wide && M >= 9) || !skinny_ok)) return LBL_PATH_GEMM_TC;
   if (skinny_ok) {
     lbl::SkinnyPlan plan;
     if (lbl::skinny_make_plan(M, N, K, -1, sm_count, &plan)) {
@@ -398,6 +402,130 @@ int lbl_w4a16_gemv_noalloc(const void* x, const int32_t* packed_w, const float* 
                         : nullptr;
   const cudaError_t err = lbl::launch_skinny(prob, plan, partials, tickets, info.status_word,
                                              (flags & LBL_FLAG_PDL) != 0, cu_stream);
+  if (err != cudaSuccess) return fail_cuda(err, "kernel launch");
+  return LBL_OK;
+}
+
+// ---------------------------------------------------------------------------------------------
+// Row-parallel (K-split) GEMV with the all-reduce fused into the kernel.
+//
+// Each rank owns an exchange buffer that its peers map through CUDA IPC.  A rank's kernel leaves
+// its FP32 result vector in its own buffer, the last CTA raises a flag in every peer's buffer,
+// waits (bounded) for the peers' flags in its own, and adds the vectors of all ranks in rank
+// order, reading the peers' memory with plain loads over NVLink.  No NCCL call, no multicast.
+// ---------------------------------------------------------------------------------------------
+size_t lbl_peer_buffer_bytes(int64_t max_n) {
+  if (max_n <= 0) return 0;
+  return lbl::kPeerBufferHeaderBytes + 2 * static_cast<size_t>(max_n) * sizeof(float);
+}
+
+int lbl_peer_buffer_create(size_t bytes, int device, void** buffer) {
+  if (buffer == nullptr || bytes < lbl::kPeerBufferHeaderBytes) return fail(LBL_ERR_INVALID, "bad peer buffer request");
+  DeviceScope scope(device);
+  if (!scope.ok()) return fail(LBL_ERR_CUDA, "cannot make device %d current", device);
+  void* ptr = nullptr;
+  cudaError_t err = cudaMalloc(&ptr, bytes);
+  if (err != cudaSuccess) return fail_cuda(err, "cudaMalloc(peer buffer)");
+  err = cudaMemset(ptr, 0, bytes);
+  if (err != cudaSuccess) {
+    cudaFree(ptr);
+    return fail_cuda(err, "cudaMemset(peer buffer)");
+  }
+  *buffer = ptr;
+  return LBL_OK;
+}
+
+int lbl_peer_buffer_export(const void* buffer, void* handle64) {
+  static_assert(sizeof(cudaIpcMemHandle_t) == 64, "IPC handle size");
+  if (buffer == nullptr || handle64 == nullptr) return fail(LBL_ERR_INVALID, "null argument");
+  cudaIpcMemHandle_t handle;
+  const cudaError_t err = cudaIpcGetMemHandle(&handle, const_cast<void*>(buffer));
+  if (err != cudaSuccess) return fail_cuda(err, "cudaIpcGetMemHandle");
+  std::memcpy(handle64, &handle, sizeof(handle));
+  return LBL_OK;
+}
+
+int lbl_peer_buffer_open(const void* handle64, int device, void** buffer) {
+  if (buffer == nullptr || handle64 == nullptr) return fail(LBL_ERR_INVALID, "null argument");
+  DeviceScope scope(device);
+  if (!scope.ok()) return fail(LBL_ERR_CUDA, "cannot make device %d current", device);
+  cudaIpcMemHandle_t handle;
+  std::memcpy(&handle, handle64, sizeof(handle));
+  void* ptr = nullptr;
+  const cudaError_t err = cudaIpcOpenMemHandle(&ptr, handle, cudaIpcMemLazyEnablePeerAccess);
+  if (err != cudaSuccess) return fail_cuda(err, "cudaIpcOpenMemHandle");
+  *buffer = ptr;
+  return LBL_OK;
+}
+
+int lbl_peer_buffer_close(void* buffer, int device) {
+  if (buffer == nullptr) return LBL_OK;
+  DeviceScope scope(device);
+  if (!scope.ok()) return fail(LBL_ERR_CUDA, "cannot make device %d current", device);
+  const cudaError_t err = cudaIpcCloseMemHandle(buffer);
+  if (err != cudaSuccess) return fail_cuda(err, "cudaIpcCloseMemHandle");
+  return LBL_OK;
+}
+
+int lbl_peer_buffer_destroy(void* buffer, int device) {
+  if (buffer == nullptr) return LBL_OK;
+  DeviceScope scope(device);
+  if (!scope.ok()) return fail(LBL_ERR_CUDA, "cannot make device %d current", device);
+  const cudaError_t err = cudaFree(buffer);
+  if (err != cudaSuccess) return fail_cuda(err, "cudaFree(peer buffer)");
+  return LBL_OK;
+}
+
+int lbl_w4a16_gemv_allreduce(const void* x, const int32_t* packed_w, const float* scales,
+                             const int32_t* zeros, void* y, int64_t N, int64_t K, int group_size,
+                             int rank, int world, void* const* buffers, int64_t buffer_capacity_n,
+                             void* workspace, size_t workspace_bytes, unsigned flags, int device,
+                             void* stream) {
+  if (group_size != 64 || K <= 0 || K % 256 != 0) {
+    return fail(LBL_ERR_UNSUPPORTED, "the fused all-reduce GEMV needs group_size=64 and K %% 256 == 0 (K=%lld)", (long long)K);
+  }
+  if (N <= 0 || N > 0x7fffffffLL || N > buffer_capacity_n) return fail(LBL_ERR_INVALID, "N=%lld does not fit the exchange buffers (capacity %lld)", (long long)N, (long long)buffer_capacity_n);
+  if (world < 1 || world > 8 || rank < 0 || rank >= world || buffers == nullptr) return fail(LBL_ERR_INVALID, "bad rank/world/buffers");
+  if (x == nullptr || packed_w == nullptr || scales == nullptr || zeros == nullptr || y == nullptr) return fail(LBL_ERR_INVALID, "null tensor pointer");
+  if (!aligned16(x) || !aligned16(packed_w) || !aligned16(scales) || !aligned16(zeros) || !aligned16(y)) return fail(LBL_ERR_INVALID, "all tensors must be 16-byte aligned");
+  for (int r = 0; r < world; ++r) {
+    if (buffers[r] == nullptr) return fail(LBL_ERR_INVALID, "exchange buffer of rank %d is null", r);
+  }
+  cudaStream_t cu_stream = static_cast<cudaStream_t>(stream);
+  DeviceScope scope(device);
+  if (!scope.ok()) return fail(LBL_ERR_CUDA, "cannot make device %d current", device);
+  DeviceInfo info;
+  const int rc = device_info(device, &info);
+  if (rc != LBL_OK) return rc;
+
+  lbl::SkinnyPlan plan;
+  if (!lbl::skinny_make_plan(1, N, K, -1, info.sm_count, &plan) || !plan.columns) {
+    return fail(LBL_ERR_UNSUPPORTED, "no decode plan for N=%lld K=%lld", (long long)N, (long long)K);
+  }
+  float* partials = nullptr;
+  int* tickets = nullptr;
+  if (plan.nsplit > 1) {
+    const size_t need = plan.partial_bytes + plan.ticket_bytes;
+    if (workspace == nullptr || workspace_bytes < need) return fail(LBL_ERR_WORKSPACE, "split-K needs %zu bytes of scratch, got %zu", need, workspace_bytes);
+    tickets = static_cast<int*>(workspace);
+    partials = reinterpret_cast<float*>(static_cast<char*>(workspace) + plan.ticket_bytes);
+  }
+  lbl::Problem prob;
+  prob.x = static_cast<const __half*>(x);
+  prob.packed = reinterpret_cast<const uint32_t*>(packed_w);
+  prob.scales = scales;
+  prob.zeros = zeros;
+  prob.y = static_cast<__half*>(y);
+  prob.M = 1;
+  prob.N = N;
+  prob.K = K;
+  lbl::PeerReduce reduce;
+  reduce.rank = rank;
+  reduce.world = world;
+  reduce.capacity_n = static_cast<int>(buffer_capacity_n);
+  for (int r = 0; r < 8; ++r) reduce.buffers[r] = r < world ? buffers[r] : nullptr;
+  const cudaError_t err = lbl::launch_gemv_decode(prob, plan, partials, tickets, info.status_word,
+                                                  (flags & LBL_FLAG_PDL) != 0, cu_stream, &reduce);
   if (err != cudaSuccess) return fail_cuda(err, "kernel launch");
   return LBL_OK;
 }

@@ -29,6 +29,7 @@ constexpr int kConsumerThreads = kConsumerWarps * 32;
 constexpr int kThreads = kConsumerThreads + 32;
 constexpr int kMaxSlots = 8;
 constexpr int kHeaderBytes = 256;
+constexpr int kMaxPeers = 8;
 
 struct DecodeParams {
   const __half* x;
@@ -41,7 +42,34 @@ struct DecodeParams {
   int row_tiles, units;
   int packed_pitch, meta_pitch, slot_bytes;
   int sx_offset, red_offset, xf_offset, ring_offset;
+  // Fused K-split all-reduce over peer memory (world == 0: off).  peers[r] is rank r's exchange
+  // buffer as mapped into this process; peers[rank] is this GPU's own.
+  int rank, world, capacity_n;
+  unsigned char* peers[kMaxPeers];
 };
+
+// Layout of an exchange buffer (see lbl_peer_buffer_* in the C ABI).
+constexpr int kPeerFlagsOffset = 128;    // world flags, one 128-byte line each: flags[src] = epoch
+constexpr int kPeerDataOffset = 2048;    // two FP32 vectors of capacity_n (epoch parity)
+constexpr int kStatusPeerWait = 110;     // status code: a peer's flag did not arrive in time
+struct PeerControl {
+  int done;            // CTAs of the running kernel that have finished their units
+  unsigned int epoch;  // number of all-reduces this GPU has completed
+};
+
+__device__ __forceinline__ void store_release_sys(unsigned int* ptr, unsigned int value) {
+  asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(ptr), "r"(value) : "memory");
+}
+__device__ __forceinline__ unsigned int load_acquire_sys(const unsigned int* ptr) {
+  unsigned int v;
+  asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(ptr) : "memory");
+  return v;
+}
+__device__ __forceinline__ float load_relaxed_sys(const float* ptr) {
+  float v;
+  asm volatile("ld.relaxed.sys.global.f32 %0, [%1];" : "=f"(v) : "l"(ptr) : "memory");
+  return v;
+}
 
 struct Header {
   uint64_t full[kMaxSlots];
@@ -202,6 +230,12 @@ __global__ void __launch_bounds__(kThreads, 2)
 #pragma unroll
   for (int i = 0; i < 4; ++i) xb[i] = make_uint4(0u, 0u, 0u, 0u);
 
+  // With the fused all-reduce this GPU's FP32 result goes to its exchange buffer (the vector of
+  // the next epoch's parity) instead of y; the last CTA to finish combines the ranks.
+  PeerControl* ctrl = nullptr;
+  float* exchange_out = nullptr;
+  unsigned int epoch = 0;
+
   int it = 0;
   int current_ks = -1;
   for (int unit = blockIdx.x; unit < p.units; unit += gridDim.x) {
@@ -211,7 +245,15 @@ __global__ void __launch_bounds__(kThreads, 2)
 
     if (ks != current_ks) {
       // Activations are the only input the previous kernel may have produced.
-      if (current_ks < 0) pdl_wait_for_previous_kernel();
+      if (current_ks < 0) {
+        pdl_wait_for_previous_kernel();
+        if (p.world > 0) {
+          ctrl = reinterpret_cast<PeerControl*>(p.peers[p.rank]);
+          epoch = *reinterpret_cast<volatile unsigned int*>(&ctrl->epoch) + 1;
+          exchange_out = reinterpret_cast<float*>(p.peers[p.rank] + kPeerDataOffset) +
+                         static_cast<size_t>(epoch & 1) * p.capacity_n;
+        }
+      }
       build_activation_operand(p, ks * p.kseg, xf, sx, tid);
       named_barrier(1, kConsumerThreads);
       current_ks = ks;
@@ -300,10 +342,12 @@ __global__ void __launch_bounds__(kThreads, 2)
         v += red[(w * kRows + row) * 4 + 2 * col] + red[(w * kRows + row) * 4 + 2 * col + 1];
       }
       if (col < p.M && n0 + row < p.N) {
-        if (p.nsplit == 1) {
-          p.y[static_cast<size_t>(col) * p.N + n0 + row] = __float2half_rn(v);
-        } else {
+        if (p.nsplit > 1) {
           p.partials[(static_cast<size_t>(ks) * p.M + col) * p.N + n0 + row] = v;
+        } else if (exchange_out != nullptr) {
+          exchange_out[n0 + row] = v;
+        } else {
+          p.y[static_cast<size_t>(col) * p.N + n0 + row] = __float2half_rn(v);
         }
       }
     }
@@ -319,20 +363,83 @@ __global__ void __launch_bounds__(kThreads, 2)
           for (int s = 0; s < p.nsplit; ++s) {
             v += __ldcg(&p.partials[(static_cast<size_t>(s) * p.M + col) * p.N + n0 + row]);
           }
-          p.y[static_cast<size_t>(col) * p.N + n0 + row] = __float2half_rn(v);
+          if (exchange_out != nullptr) {
+            exchange_out[n0 + row] = v;
+          } else {
+            p.y[static_cast<size_t>(col) * p.N + n0 + row] = __float2half_rn(v);
+          }
         }
         if (tid == 0) p.tickets[rt] = 0;
       }
     }
     named_barrier(1, kConsumerThreads);
   }
+
+  if (p.world == 0) return;
+  // ---- fused all-reduce: the last CTA of this GPU tells its peers, waits for theirs, and adds the
+  // ranks' vectors in rank order (so every rank computes the same bits) ---------------------------
+  if (ctrl == nullptr) {  // a CTA without units still has to be counted
+    pdl_wait_for_previous_kernel();
+    ctrl = reinterpret_cast<PeerControl*>(p.peers[p.rank]);
+    epoch = *reinterpret_cast<volatile unsigned int*>(&ctrl->epoch) + 1;
+  }
+  __threadfence();
+  named_barrier(1, kConsumerThreads);
+  if (tid == 0) hdr->ticket = atomicAdd(&ctrl->done, 1);
+  named_barrier(1, kConsumerThreads);
+  if (hdr->ticket != static_cast<int>(gridDim.x) - 1) return;
+  __threadfence();
+  if (tid < p.world && tid != p.rank) {
+    // Publish: this GPU's vector for `epoch` is complete.  The flag lives in the peer's buffer, so
+    // that every GPU polls its own memory.
+    __threadfence_system();
+    store_release_sys(reinterpret_cast<unsigned int*>(p.peers[tid] + kPeerFlagsOffset + p.rank * 128), epoch);
+    const unsigned int* mine =
+        reinterpret_cast<const unsigned int*>(p.peers[p.rank] + kPeerFlagsOffset + tid * 128);
+    const long long start = clock64();
+    while (static_cast<int>(load_acquire_sys(mine) - epoch) < 0) {
+      if (clock64() - start > kWaitLimitCycles) {  // bounded: report and go on
+        atomicCAS(p.status, 0, kStatusPeerWait);
+        break;
+      }
+    }
+  }
+  named_barrier(1, kConsumerThreads);
+  const size_t vec = static_cast<size_t>(epoch & 1) * p.capacity_n;
+  for (int n = tid; n < p.N; n += kConsumerThreads) {
+    float v = 0.0f;
+    for (int r = 0; r < p.world; ++r) {
+      v += load_relaxed_sys(reinterpret_cast<const float*>(p.peers[r] + kPeerDataOffset) + vec + n);
+    }
+    p.y[n] = __float2half_rn(v);
+  }
+  if (tid == 0) {
+    ctrl->done = 0;
+    *reinterpret_cast<volatile unsigned int*>(&ctrl->epoch) = epoch;
+  }
 }
 
 }  // namespace
 
 cudaError_t launch_gemv_decode(const Problem& p, const SkinnyPlan& plan, float* partials,
-                               int* tickets, int* status_word, bool pdl, cudaStream_t stream) {
+                               int* tickets, int* status_word, bool pdl, cudaStream_t stream,
+                               const PeerReduce* reduce) {
+  static_assert(kPeerDataOffset == static_cast<int>(kPeerBufferHeaderBytes), "layout mismatch");
   DecodeParams kp;
+  kp.rank = 0;
+  kp.world = 0;
+  kp.capacity_n = 0;
+  for (int i = 0; i < kMaxPeers; ++i) kp.peers[i] = nullptr;
+  if (reduce != nullptr) {
+    if (p.M != 1 || reduce->world < 1 || reduce->world > kMaxPeers || reduce->rank < 0 ||
+        reduce->rank >= reduce->world || p.N > reduce->capacity_n) {
+      return cudaErrorInvalidValue;
+    }
+    kp.rank = reduce->rank;
+    kp.world = reduce->world;
+    kp.capacity_n = reduce->capacity_n;
+    for (int i = 0; i < reduce->world; ++i) kp.peers[i] = static_cast<unsigned char*>(reduce->buffers[i]);
+  }
   kp.x = p.x;
   kp.y = p.y;
   kp.partials = partials;

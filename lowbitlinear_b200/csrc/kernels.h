@@ -55,8 +55,16 @@ bool skinny_supports(int64_t M, int64_t N, int64_t K);
 bool skinny_make_plan(int64_t M, int64_t N, int64_t K, int want_split, int sm_count,
                       SkinnyPlan* plan);
 bool skinny_encode_maps(const Problem& p, const SkinnyPlan& plan, ::CUtensorMap_st* maps);
+// Fused K-split all-reduce of the decode GEMV: exchange buffers of all ranks as mapped into this
+// process (buffers[rank] is this GPU's own), each holding two FP32 vectors of capacity_n.
+struct PeerReduce {
+  int rank, world, capacity_n;
+  void* buffers[8];
+};
+constexpr size_t kPeerBufferHeaderBytes = 2048;
 cudaError_t launch_gemv_decode(const Problem& p, const SkinnyPlan& plan, float* partials,
-                               int* tickets, int* status_word, bool pdl, cudaStream_t stream);
+                               int* tickets, int* status_word, bool pdl, cudaStream_t stream,
+                               const PeerReduce* reduce = nullptr);
 cudaError_t launch_skinny(const Problem& p, const SkinnyPlan& plan, float* partials, int* tickets,
                           int* status_word, bool pdl, cudaStream_t stream);
 

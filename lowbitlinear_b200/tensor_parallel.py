@@ -12,7 +12,12 @@ tensors gives exactly the bits that quantising the cut weight would give:
   activation and the partial outputs are summed with an all-reduce.
 
 One process per GPU; ``torch.distributed`` (NCCL on GPUs, gloo on CPU) carries the collectives.
+For decode (M = 1) the K-split all-reduce can be fused into the GEMV kernel instead: each rank
+leaves its FP32 partial vector in an exchange buffer that its peers map through CUDA IPC, and
+the kernel's last CTA adds the ranks' vectors over NVLink (``PeerExchange``).
 """
+import ctypes
+
 import torch
 import torch.distributed as dist
 
@@ -51,6 +56,55 @@ def shard_row_parallel(layer, rank, world_size):
         layer.zeros[:, groups].contiguous(), gs, in_features=part)
 
 
+class PeerExchange:
+    """Exchange buffers of all ranks of ``group`` for the fused K-split all-reduce (same node,
+    one process per GPU).  Creating one is a collective call.  ``max_n`` bounds ``out_features``."""
+
+    def __init__(self, max_n, device, group=None):
+        from . import _extension
+
+        lib = _extension.native()
+        self._lib = lib
+        self.rank, self.world = _world(group)
+        self.capacity_n = int(max_n)
+        self.device = torch.device(device)
+        size = lib.lbl_peer_buffer_bytes(self.capacity_n)
+        own = ctypes.c_void_p()
+        self._check(lib.lbl_peer_buffer_create(size, self.device.index, ctypes.byref(own)))
+        handle = (ctypes.c_ubyte * 64)()
+        self._check(lib.lbl_peer_buffer_export(own, handle))
+        handles = [None] * self.world
+        dist.all_gather_object(handles, bytes(handle), group=group)
+        self._own = own
+        self._opened = []
+        pointers = []
+        for r, raw in enumerate(handles):
+            if r == self.rank:
+                pointers.append(own.value)
+                continue
+            mapped = ctypes.c_void_p()
+            buf = (ctypes.c_ubyte * 64).from_buffer_copy(raw)
+            self._check(lib.lbl_peer_buffer_open(buf, self.device.index, ctypes.byref(mapped)))
+            self._opened.append(mapped)
+            pointers.append(mapped.value)
+        self.pointers = (ctypes.c_void_p * self.world)(*pointers)
+        dist.barrier(group=group)  # every rank has mapped every buffer before the first kernel
+
+    def _check(self, rc):
+        if rc != 0:
+            raise RuntimeError(self._lib.lbl_last_error().decode())
+
+    def close(self):
+        """Unmap the peers' buffers and free this rank's.  Call it on every rank, after the
+        last kernel that uses the exchange has finished."""
+        for mapped in self._opened:
+            self._lib.lbl_peer_buffer_close(mapped, self.device.index)
+        self._opened = []
+        if self._own is not None:
+            self._lib.lbl_peer_buffer_destroy(self._own, self.device.index)
+            self._own = None
+
+
 class ColumnParallelLinear(torch.nn.Module):
     """N-split linear.  ``forward(x)`` takes the full activation ``[M, K]`` and returns this
     rank's ``[M, N / g]`` block, or the full ``[M, N]`` after an all-gather when
@@ -86,22 +140,34 @@ class RowParallelLinear(torch.nn.Module):
     activation (or the full ``[M, K]`` with ``input_is_parallel=False``) and returns the
     all-reduced ``[M, N]``."""
 
-    def __init__(self, shard, group=None, input_is_parallel=True):
+    def __init__(self, shard, group=None, input_is_parallel=True, exchange=None):
         super().__init__()
         self.shard = shard
         self.group = group
         self.input_is_parallel = input_is_parallel
+        self.exchange = exchange  # PeerExchange: fuse the all-reduce into the decode kernel
 
     @classmethod
-    def from_full(cls, layer, group=None, input_is_parallel=True):
+    def from_full(cls, layer, group=None, input_is_parallel=True, exchange=None):
         rank, world = _world(group)
-        return cls(shard_row_parallel(layer, rank, world), group, input_is_parallel)
+        return cls(shard_row_parallel(layer, rank, world), group, input_is_parallel, exchange)
+
+    def _fused(self, x):
+        shard = self.shard
+        return (self.exchange is not None and x.is_cuda and x.shape[0] == 1 and shard.group_size == 64
+                and shard.in_features % 256 == 0 and shard.out_features <= self.exchange.capacity_n
+                and x.dtype == torch.float16 and x.is_contiguous())
 
     def forward(self, x):
         rank, world = _world(self.group)
         if not self.input_is_parallel:
             part = self.shard.in_features
             x = x[:, rank * part:(rank + 1) * part].contiguous()
+        if self._fused(x):
+            from . import _ops
+
+            return _ops.gemv_allreduce(x, self.shard.packed_weight, self.shard.scales,
+                                       self.shard.zeros, self.exchange)
         y = self.shard(x)
         if world > 1:
             dist.all_reduce(y, op=dist.ReduceOp.SUM, group=self.group)

@@ -125,3 +125,62 @@ def test_two_nccl_ranks_on_gpus(tmp_path):
     world = 2
     mp.spawn(_worker, args=(world, _free_port(), "nccl", str(tmp_path)), nprocs=world, join=True)
     _check(tmp_path, world)
+
+
+def _fused_worker(rank, world, port, result_dir):
+    """K-split decode GEMV with the all-reduce fused into the kernel (peer exchange buffers)."""
+    from lowbitlinear_b200 import _ops
+    from lowbitlinear_b200.tensor_parallel import PeerExchange
+
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), NCCL_NVLS_ENABLE="0")
+    torch.cuda.set_device(rank)
+    device = torch.device("cuda", rank)
+    dist.init_process_group("nccl", rank=rank, world_size=world)
+    try:
+        n, k = 512, 2048 * world
+        weight, x = _layer(n, k, seed=9, std=0.05)
+        full = QuantizedLinear.from_float(weight)
+        exchange = PeerExchange(max_n=n, device=device)
+        on_gpu = QuantizedLinear.from_float(weight).to(device)  # Module.to moves buffers in place
+        row = RowParallelLinear.from_full(on_gpu, exchange=exchange)
+        part = k // world
+        outputs, expected = [], []
+        for i in range(6):  # consecutive calls alternate between the two exchange vectors
+            xi = (x[:1] * (1.0 + 0.25 * i)).half()
+            outputs.append(row(xi[:, rank * part:(rank + 1) * part].contiguous().to(device)))
+            expected.append(full(xi).float())
+        torch.cuda.synchronize()
+        assert _ops.device_status(device) == 0, "a bounded wait expired"
+        dist.barrier()
+        exchange.close()
+        np.savez(Path(result_dir) / f"fused{rank}.npz",
+                 outputs=torch.cat(outputs).float().cpu().numpy(), expected=torch.cat(expected).numpy())
+    finally:
+        dist.destroy_process_group()
+
+
+def _check_fused(result_dir, world):
+    first = None
+    for rank in range(world):
+        r = np.load(Path(result_dir) / f"fused{rank}.npz")
+        # FP32 partial sums are added across ranks, one FP16 rounding at the end.
+        np.testing.assert_allclose(r["outputs"], r["expected"], atol=2e-3, rtol=1e-3)
+        if first is None:
+            first = r["outputs"]
+        assert np.array_equal(r["outputs"], first), "ranks must agree bit for bit"
+
+
+@pytest.mark.gpu
+def test_fused_allreduce_single_rank(tmp_path):
+    if not torch.cuda.is_available():
+        pytest.skip("no CUDA GPU")
+    mp.spawn(_fused_worker, args=(1, _free_port(), str(tmp_path)), nprocs=1, join=True)
+    _check_fused(tmp_path, 1)
+
+
+@pytest.mark.gpu
+def test_fused_allreduce_two_ranks(tmp_path):
+    if torch.cuda.device_count() < 2:
+        pytest.skip("needs two GPUs")
+    mp.spawn(_fused_worker, args=(2, _free_port(), str(tmp_path)), nprocs=2, join=True)
+    _check_fused(tmp_path, 2)
