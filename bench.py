@@ -164,15 +164,27 @@ def build_stack(m, device, rank, world, host_layer0):
     return layers, xs
 
 
+EXCHANGE = None  # PeerExchange of a tensor-parallel decode run: all-reduce fused into the GEMV
+
+
 def run_stack(layers, xs, world):
-    """One pass over the stack through the public operators; returns the outputs."""
+    """One pass over the stack through the public operators; returns the outputs.  Between
+    tensor-parallel ranks the K-split Down projection ends in an all-reduce: fused into the
+    decode kernel over peer memory when an exchange is set up, NCCL otherwise."""
     import torch.distributed as dist
+
+    from lowbitlinear_b200 import _ops
 
     outs = []
     for (name, layer), x in zip(layers, xs):
-        y = layer(x)
         if world > 1 and name == "down":
-            dist.all_reduce(y)
+            if EXCHANGE is not None and x.shape[0] == 1:
+                y = _ops.gemv_allreduce(x, layer.packed_weight, layer.scales, layer.zeros, EXCHANGE)
+            else:
+                y = layer(x)
+                dist.all_reduce(y)
+        else:
+            y = layer(x)
         outs.append(y)
     return outs
 
@@ -335,6 +347,10 @@ def run_ours(args):
             host_layer0 = [host_layer0_map[i] for i in range(4)]
 
     with torch.inference_mode():
+        global EXCHANGE
+        if world > 1 and args.workload == "decode" and args.fused_allreduce:
+            from lowbitlinear_b200.tensor_parallel import PeerExchange
+            EXCHANGE = PeerExchange(max_n=4096, device=device)
         note("building the stack")
         layers, xs = build_stack(m, device, rank, world, host_layer0)
         torch.cuda.synchronize()
@@ -370,10 +386,10 @@ def run_ours(args):
 
         # ---- capture one step as a CUDA graph ---------------------------------------------------
         note("capturing the step")
-        # Between tensor-parallel ranks the kernels alternate with NCCL kernels; a dependent
-        # launch that holds SM resources while it waits for a collective could starve it, so
-        # programmatic dependent launch is used on a single GPU only.
-        use_pdl = bool(args.pdl) and world == 1
+        # When tensor-parallel ranks use NCCL, the kernels alternate with NCCL kernels; a
+        # dependent launch that holds SM resources while it waits for a collective could starve
+        # it, so programmatic dependent launch is used only when no NCCL kernel is in the graph.
+        use_pdl = bool(args.pdl) and (world == 1 or EXCHANGE is not None)
         _ops.set_programmatic_dependent_launch(use_pdl)
         side = torch.cuda.Stream()
         side.wait_stream(torch.cuda.current_stream())
@@ -512,7 +528,10 @@ def run_ours(args):
         "steps": args.steps, "warmup": max(args.warmup, 3), "ms_per_step": ms_per_step,
         "higher_is_better": True, "scaling": "strong", "vs_baseline": None,
         "dtype": "f16 activations x int4 weights, f32 accumulate", "data": "synthetic",
-        "config": config_of(args.workload, m, world, args.pdl and world == 1),
+        "config": dict(config_of(args.workload, m, world, args.pdl and (world == 1 or EXCHANGE is not None)),
+                       allreduce=("none" if world == 1 else
+                                  "fused into the Down GEMV over NVLink peer memory" if EXCHANGE is not None
+                                  else "NCCL")),
         "roofline": roofline, "cpu_baseline": cpu_baseline, "clocks": clocks,
         "e2e": {"value": amount / (e2e_ms * 1e-3), "unit": unit, "ms_per_step": e2e_ms,
                 "h2d_bytes_per_step": int(host_x.numel() * 2 * chunks_per_step),
@@ -534,6 +553,8 @@ def main():
     parser.add_argument("--impl", choices=("ours", "reference"), default="ours")
     parser.add_argument("--workload", choices=("decode", "prefill"), default="decode")
     parser.add_argument("--pdl", type=int, default=1)
+    parser.add_argument("--fused-allreduce", type=int, default=1,
+                        help="tensor-parallel decode: fuse the K-split all-reduce into the GEMV (0: NCCL)")
     args = parser.parse_args()
     if args.impl == "reference":
         if args.steps == 200:

@@ -485,6 +485,7 @@ int lbl_w4a16_gemv_allreduce(const void* x, const int32_t* packed_w, const float
     return fail(LBL_ERR_UNSUPPORTED, "the fused all-reduce GEMV needs group_size=64 and K %% 256 == 0 (K=%lld)", (long long)K);
   }
   if (N <= 0 || N > 0x7fffffffLL || N > buffer_capacity_n) return fail(LBL_ERR_INVALID, "N=%lld does not fit the exchange buffers (capacity %lld)", (long long)N, (long long)buffer_capacity_n);
+  if (buffer_capacity_n % 4 != 0) return fail(LBL_ERR_INVALID, "buffer_capacity_n must be a multiple of 4");
   if (world < 1 || world > 8 || rank < 0 || rank >= world || buffers == nullptr) return fail(LBL_ERR_INVALID, "bad rank/world/buffers");
   if (x == nullptr || packed_w == nullptr || scales == nullptr || zeros == nullptr || y == nullptr) return fail(LBL_ERR_INVALID, "null tensor pointer");
   if (!aligned16(x) || !aligned16(packed_w) || !aligned16(scales) || !aligned16(zeros) || !aligned16(y)) return fail(LBL_ERR_INVALID, "all tensors must be 16-byte aligned");

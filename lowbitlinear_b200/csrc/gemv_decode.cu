@@ -65,6 +65,15 @@ __device__ __forceinline__ unsigned int load_acquire_sys(const unsigned int* ptr
   asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(ptr) : "memory");
   return v;
 }
+__device__ __forceinline__ float4 load_relaxed_sys_v4(const float* ptr) {
+  float4 v;
+  // volatile keeps it behind the flag wait; no memory clobber, so independent loads can be issued
+  // back to back before their values are used.
+  asm volatile("ld.relaxed.sys.global.v4.f32 {%0, %1, %2, %3}, [%4];"
+               : "=f"(v.x), "=f"(v.y), "=f"(v.z), "=f"(v.w)
+               : "l"(ptr));
+  return v;
+}
 __device__ __forceinline__ float load_relaxed_sys(const float* ptr) {
   float v;
   asm volatile("ld.relaxed.sys.global.f32 %0, [%1];" : "=f"(v) : "l"(ptr) : "memory");
@@ -406,7 +415,45 @@ __global__ void __launch_bounds__(kThreads, 2)
   }
   named_barrier(1, kConsumerThreads);
   const size_t vec = static_cast<size_t>(epoch & 1) * p.capacity_n;
-  for (int n = tid; n < p.N; n += kConsumerThreads) {
+  // The loads of two chunks from all ranks are issued before any is used: one NVLink round trip
+  // per pair of chunks instead of one per load.
+  const int n4 = p.N & ~3;
+  for (int n = tid * 4; n < n4; n += kConsumerThreads * 8) {
+    const int n_next = n + kConsumerThreads * 4;
+    float4 part[2][kMaxPeers];
+#pragma unroll
+    for (int c = 0; c < 2; ++c) {
+      const int nc = c == 0 ? n : n_next;
+#pragma unroll
+      for (int r = 0; r < kMaxPeers; ++r) {
+        if (r < p.world && nc < n4) {
+          part[c][r] = load_relaxed_sys_v4(reinterpret_cast<const float*>(p.peers[r] + kPeerDataOffset) + vec + nc);
+        }
+      }
+    }
+#pragma unroll
+    for (int c = 0; c < 2; ++c) {
+      const int nc = c == 0 ? n : n_next;
+      if (nc >= n4) continue;
+      float4 v = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+#pragma unroll
+      for (int r = 0; r < kMaxPeers; ++r) {
+        if (r < p.world) {
+          v.x += part[c][r].x;
+          v.y += part[c][r].y;
+          v.z += part[c][r].z;
+          v.w += part[c][r].w;
+        }
+      }
+      __half2 lo = __floats2half2_rn(v.x, v.y);
+      __half2 hi = __floats2half2_rn(v.z, v.w);
+      uint2 out;
+      out.x = *reinterpret_cast<uint32_t*>(&lo);
+      out.y = *reinterpret_cast<uint32_t*>(&hi);
+      *reinterpret_cast<uint2*>(p.y + nc) = out;
+    }
+  }
+  for (int n = n4 + tid; n < p.N; n += kConsumerThreads) {
     float v = 0.0f;
     for (int r = 0; r < p.world; ++r) {
       v += load_relaxed_sys(reinterpret_cast<const float*>(p.peers[r] + kPeerDataOffset) + vec + n);
