@@ -224,6 +224,22 @@ def linear_forced(X, packed_w, scales, zeros, path, op=1, flags=None):
     return Y, taken.value
 
 
+def linear_out(X, packed_w, scales, zeros, out, op=None):
+    """Dispatcher call that writes into a caller-provided ``out`` ``[M, N]`` (FP16, contiguous,
+    16-byte aligned) instead of allocating: what a CUDA-graph runner with static buffers needs.
+    ``op`` defaults to the operator ``QuantizedLinear.forward`` would pick."""
+    m, k = X.shape
+    n = packed_w.size(0)
+    if op is None:
+        op = 0 if (m == 1 and k % 64 == 0 and n % 128 == 0) else 1
+    stream = torch.cuda.current_stream(X.device).cuda_stream
+    ws, ws_bytes = _workspace(X.device, stream, m, n, k)
+    _check(_lib.lbl_w4a16_linear(X.data_ptr(), packed_w.data_ptr(), scales.data_ptr(),
+                                 zeros.data_ptr(), out.data_ptr(), m, n, k, op, PATH_AUTO, ws, ws_bytes,
+                                 _flags, X.device.index, stream, None))
+    return out
+
+
 def gemv_allreduce(x, packed_w, scales, zeros, exchange):
     """K-split GEMV with the all-reduce fused into the kernel: ``x`` is this rank's ``[1, K/g]``
     slice, the weights its column slice; returns the full ``[1, N]`` (identical on every rank).

@@ -1,0 +1,84 @@
+"""CUDA-graph runner for a sequence of quantised linears with static buffers.
+
+``QuantizedLinear.forward`` re-validates its state and allocates its output on every call
+(as the reference does, ``lowbitlinear/linear.py:95-129``); at decode sizes that host work costs
+more than the kernels.  ``GraphedLinears`` validates once, captures the forward of every layer
+into one CUDA graph (``torch.cuda.CUDAGraph``: streams and graphs, no tracing compiler), and
+replays it on demand:
+
+    runner = GraphedLinears(layers, m=1)            # layers: list of QuantizedLinear on one GPU
+    runner.run(host_x, host_y)                      # pinned flat FP16 buffers in, out
+
+Each layer has its own activation ``[m, in_features]`` (views of one flat device buffer, in
+layer order) and writes its ``[m, out_features]`` result into a flat output buffer, so one
+host-to-device copy feeds a replay and one device-to-host copy returns everything.  The layers
+are independent here; a model runner would capture its own sequence the same way.
+"""
+import torch
+
+from . import _ops
+from ._extension import load_cuda_extension
+from .linear import _validate_packed_weight
+
+
+class GraphedLinears:
+    def __init__(self, layers, m=1, programmatic_dependent_launch=True):
+        load_cuda_extension(required=True)
+        layers = list(layers)
+        if not layers:
+            raise ValueError("no layers")
+        device = layers[0].packed_weight.device
+        for layer in layers:
+            _validate_packed_weight(layer.packed_weight, layer.scales, layer.zeros, layer.group_size,
+                                    layer.in_features)
+            if layer.group_size != 64 or not layer.packed_weight.is_cuda or layer.packed_weight.device != device:
+                raise ValueError("GraphedLinears needs CUDA layers with group_size 64 on one device")
+        self.layers = layers
+        self.m = m
+        self.device = device
+        # Offsets are multiples of 8 elements so that every view stays 16-byte aligned.
+        pad = lambda v: (v + 7) // 8 * 8
+        self.x_offsets, self.y_offsets = [], []
+        x_total = y_total = 0
+        for layer in layers:
+            self.x_offsets.append(x_total)
+            self.y_offsets.append(y_total)
+            x_total += pad(m * layer.in_features)
+            y_total += pad(m * layer.out_features)
+        self.x_flat = torch.zeros(x_total, dtype=torch.float16, device=device)
+        self.y_flat = torch.zeros(y_total, dtype=torch.float16, device=device)
+        self.xs = [self.x_flat[o:o + m * l.in_features].view(m, l.in_features)
+                   for o, l in zip(self.x_offsets, layers)]
+        self.ys = [self.y_flat[o:o + m * l.out_features].view(m, l.out_features)
+                   for o, l in zip(self.y_offsets, layers)]
+        self.stream = torch.cuda.Stream(device=device)
+        self.graph = torch.cuda.CUDAGraph()
+        previous = _ops._flags
+        _ops.set_programmatic_dependent_launch(programmatic_dependent_launch)
+        try:
+            self.stream.wait_stream(torch.cuda.current_stream(device))
+            with torch.cuda.stream(self.stream):
+                self._forward()  # warm-up: creates the per-stream scratch outside the capture
+            torch.cuda.current_stream(device).wait_stream(self.stream)
+            torch.cuda.synchronize(device)
+            with torch.cuda.graph(self.graph, stream=self.stream):
+                self._forward()
+        finally:
+            _ops._flags = previous
+
+    def _forward(self):
+        for layer, x, y in zip(self.layers, self.xs, self.ys):
+            _ops.linear_out(x, layer.packed_weight, layer.scales, layer.zeros, y)
+
+    def replay(self):
+        """Replay on the current stream with whatever ``x_flat`` holds; results in ``y_flat``."""
+        self.graph.replay()
+
+    def run(self, host_x, host_y):
+        """``host_x`` -> device, replay, device -> ``host_y`` (flat FP16 tensors, ideally pinned),
+        then wait for the copy.  Layout: ``x_offsets`` / ``y_offsets`` in elements."""
+        self.x_flat.copy_(host_x, non_blocking=True)
+        self.graph.replay()
+        host_y.copy_(self.y_flat, non_blocking=True)
+        torch.cuda.current_stream(self.device).synchronize()
+        return host_y
