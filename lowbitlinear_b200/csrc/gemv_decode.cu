@@ -28,8 +28,9 @@ constexpr int kConsumerWarps = 8;
 constexpr int kConsumerThreads = kConsumerWarps * 32;
 constexpr int kThreads = kConsumerThreads + 32;
 constexpr int kMaxSlots = 8;
-constexpr int kHeaderBytes = 256;
+constexpr int kHeaderBytes = 384;
 constexpr int kMaxPeers = 8;
+constexpr int kRedBuffers = 8;  // unit results wait here for their reduction; see the unit loop
 
 struct DecodeParams {
   const __half* x;
@@ -83,9 +84,10 @@ __device__ __forceinline__ float load_relaxed_sys(const float* ptr) {
 struct Header {
   uint64_t full[kMaxSlots];
   uint64_t empty[kMaxSlots];
+  uint64_t red_full[kRedBuffers];  // all eight warps have deposited their part of a unit
   int abort_flag;
   int ticket;
-  int pad[14];
+  int pad[2];
   uint4 zeros[4];  // B operand of the lanes that feed no activation column
 };
 static_assert(sizeof(Header) <= kHeaderBytes, "header does not fit");
@@ -175,6 +177,7 @@ __global__ void __launch_bounds__(kThreads, 2)
       mbar_init(&hdr->full[s], 1);
       mbar_init(&hdr->empty[s], kConsumerWarps);
     }
+    for (int b = 0; b < kRedBuffers; ++b) mbar_init(&hdr->red_full[b], kConsumerWarps);
     hdr->abort_flag = 0;
     hdr->ticket = 0;
     for (int i = 0; i < 4; ++i) hdr->zeros[i] = make_uint4(0u, 0u, 0u, 0u);
@@ -245,7 +248,53 @@ __global__ void __launch_bounds__(kThreads, 2)
   float* exchange_out = nullptr;
   unsigned int epoch = 0;
 
+  // Reduction of the CTA's j-th unit by one warp: adds the eight warps' parts (and the two group
+  // parities) in a fixed order; lane = activation row * 16 + weight row.
+  auto reduce_unit = [&](int j) {
+    const int unit = blockIdx.x + j * gridDim.x;
+    const int ks = unit / p.row_tiles;
+    const int rt = unit - ks * p.row_tiles;
+    const int n0 = rt * kRows;
+    const int buffer = j & (kRedBuffers - 1);
+    mbar_wait_bounded(&hdr->red_full[buffer], (j / kRedBuffers) & 1, abort_flag, p.status,
+                      kStatusSkinnyFullWait);
+    const float* parts = red + buffer * kConsumerWarps * (kRows * 4);
+    const int row = lane & 15;
+    const int col = lane >> 4;
+    float v = 0.0f;
+#pragma unroll
+    for (int w = 0; w < kConsumerWarps; ++w) {
+      v += parts[w * (kRows * 4) + row * 4 + 2 * col] + parts[w * (kRows * 4) + row * 4 + 2 * col + 1];
+    }
+    const bool valid = col < p.M && n0 + row < p.N;
+    if (p.nsplit > 1) {
+      if (valid) p.partials[(static_cast<size_t>(ks) * p.M + col) * p.N + n0 + row] = v;
+      __threadfence();
+      __syncwarp();
+      int ticket = 0;
+      if (lane == 0) ticket = atomicAdd(&p.tickets[rt], 1);
+      ticket = __shfl_sync(0xffffffffu, ticket, 0);
+      if (ticket != p.nsplit - 1) return;
+      __threadfence();
+      if (valid) {
+        v = 0.0f;
+        for (int s = 0; s < p.nsplit; ++s) {
+          v += __ldcg(&p.partials[(static_cast<size_t>(s) * p.M + col) * p.N + n0 + row]);
+        }
+      }
+      if (lane == 0) p.tickets[rt] = 0;
+    }
+    if (valid) {
+      if (exchange_out != nullptr) {
+        exchange_out[n0 + row] = v;
+      } else {
+        p.y[static_cast<size_t>(col) * p.N + n0 + row] = __float2half_rn(v);
+      }
+    }
+  };
+
   int it = 0;
+  int seq = 0;  // units this CTA has computed
   int current_ks = -1;
   for (int unit = blockIdx.x; unit < p.units; unit += gridDim.x) {
     const int ks = unit / p.row_tiles;
@@ -338,51 +387,21 @@ __global__ void __launch_bounds__(kThreads, 2)
       if (lane == 0) mbar_arrive(&hdr->empty[slot]);
     }
 
-    // ---- reduction of the unit over warps and over the two group parities, fixed order -------
-    red[(warp * kRows + g) * 4 + t] = acc_a;
-    red[(warp * kRows + g + 8) * 4 + t] = acc_b;
-    named_barrier(1, kConsumerThreads);
-    const int col = tid >> 4;  // activation row, valid for tid < 32
-    const int row = tid & 15;
-    if (tid < 2 * kRows) {
-      float v = 0.0f;
-#pragma unroll
-      for (int w = 0; w < kConsumerWarps; ++w) {
-        v += red[(w * kRows + row) * 4 + 2 * col] + red[(w * kRows + row) * 4 + 2 * col + 1];
-      }
-      if (col < p.M && n0 + row < p.N) {
-        if (p.nsplit > 1) {
-          p.partials[(static_cast<size_t>(ks) * p.M + col) * p.N + n0 + row] = v;
-        } else if (exchange_out != nullptr) {
-          exchange_out[n0 + row] = v;
-        } else {
-          p.y[static_cast<size_t>(col) * p.N + n0 + row] = __float2half_rn(v);
-        }
-      }
+    // ---- deposit this warp's part of the unit.  Nobody waits here: the unit is reduced by one
+    // warp at the end of the *next* unit, when the other warps have long deposited theirs, so the
+    // warps of a CTA never run in lockstep.  kRedBuffers bounds how far they may drift apart; the
+    // ring of stages (at most 6 slots) keeps them closer than that. ---------------------------------
+    {
+      float* mine = red + ((seq & (kRedBuffers - 1)) * kConsumerWarps + warp) * (kRows * 4);
+      mine[g * 4 + t] = acc_a;
+      mine[(g + 8) * 4 + t] = acc_b;
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&hdr->red_full[seq & (kRedBuffers - 1)]);
     }
-    if (p.nsplit > 1) {
-      __threadfence();
-      named_barrier(1, kConsumerThreads);
-      if (tid == 0) hdr->ticket = atomicAdd(&p.tickets[rt], 1);
-      named_barrier(1, kConsumerThreads);
-      if (hdr->ticket == p.nsplit - 1) {
-        __threadfence();
-        if (tid < 2 * kRows && col < p.M && n0 + row < p.N) {
-          float v = 0.0f;
-          for (int s = 0; s < p.nsplit; ++s) {
-            v += __ldcg(&p.partials[(static_cast<size_t>(s) * p.M + col) * p.N + n0 + row]);
-          }
-          if (exchange_out != nullptr) {
-            exchange_out[n0 + row] = v;
-          } else {
-            p.y[static_cast<size_t>(col) * p.N + n0 + row] = __float2half_rn(v);
-          }
-        }
-        if (tid == 0) p.tickets[rt] = 0;
-      }
-    }
-    named_barrier(1, kConsumerThreads);
+    if (seq > 0 && warp == ((seq - 1) & (kConsumerWarps - 1))) reduce_unit(seq - 1);
+    ++seq;
   }
+  if (seq > 0 && warp == ((seq - 1) & (kConsumerWarps - 1))) reduce_unit(seq - 1);
 
   if (p.world == 0) return;
   // ---- fused all-reduce: the last CTA of this GPU tells its peers, waits for theirs, and adds the

@@ -42,7 +42,7 @@ constexpr int kConsumerWarps = 8;
 constexpr int kConsumerThreads = kConsumerWarps * 32;
 constexpr int kThreads = kConsumerThreads + 32;
 constexpr int kMaxSlots = 8;
-constexpr int kHeaderBytes = 256;
+constexpr int kHeaderBytes = 384;
 constexpr int kMaxStageK = 2048;
 constexpr int kXfBudgetBytes = 64 * 1024;   // activation operand kept in shared memory
 constexpr int kSmemBudgetTwoCtas = 110 * 1024;
@@ -466,7 +466,8 @@ bool skinny_make_plan(int64_t M, int64_t N, int64_t K, int want_split, int sm_co
   const int slot_bytes = kRows * packed_pitch + 2 * kRows * meta_pitch;
   auto round128 = [](int v) { return (v + 127) / 128 * 128; };
   const int sx_bytes = round128(columns ? (kseg / 64) * 2 * 4 : (kseg / 64) * mc * 4);
-  const int red_bytes = round128(columns ? kConsumerWarps * kRows * 4 * 4 : kConsumerWarps * kRows * mc * 4);
+  // Decode form: eight buffers of unit results (see gemv_decode.cu), general form: one.
+  const int red_bytes = round128(columns ? 8 * kConsumerWarps * kRows * 4 * 4 : kConsumerWarps * kRows * mc * 4);
   const int xf_bytes = round128(m * kseg * 2);
   const int fixed = kHeaderBytes + sx_bytes + red_bytes + xf_bytes;
 
@@ -478,7 +479,7 @@ bool skinny_make_plan(int64_t M, int64_t N, int64_t K, int want_split, int sm_co
     per_sm = 1;
   }
   int slots = (budget - fixed) / slot_bytes;
-  slots = std::min(slots, std::min(kMaxSlots, std::max(2, env_int("LBL_SKINNY_SLOTS", kMaxSlots))));
+  slots = std::min(slots, std::min(columns ? 6 : kMaxSlots, std::max(2, env_int("LBL_SKINNY_SLOTS", kMaxSlots))));
   if (slots < 2) return false;
 
   const int64_t units = static_cast<int64_t>(row_tiles) * nsplit;
