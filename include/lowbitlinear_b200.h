@@ -144,6 +144,19 @@ int lbl_w4a16_gemv_allreduce(const void* x, const int32_t* packed_w, const float
                              void* workspace, size_t workspace_bytes, unsigned flags, int device,
                              void* stream);
 
+/* ---- Quantiser -----------------------------------------------------------------------------
+ * Replaces QuantizedLinear.from_float's quantize_int4 + pack_int4 pair
+ * (lowbitlinear/linear.py:55-76, lowbitlinear/quantization.py:33-86 and :112-141) for weights
+ * that are already on the GPU: one kernel reads weight [N, K] (FP16, or FP32 when
+ * weight_is_fp32 != 0; row-major contiguous) and writes packed_w [N, ceil(K/8)],
+ * scales [N, ceil(K/64)] and zeros [N, ceil(K/64)].  The arithmetic is the reference's CPU
+ * arithmetic (IEEE FP32 division, round half to even, no fused multiply-add), so all three
+ * outputs are bit-identical to the reference run on CPU tensors; columns past K pack as level 0.
+ * group_size must be 64 (LBL_ERR_UNSUPPORTED otherwise); any N >= 0 and K >= 1. */
+int lbl_w4a16_quantize(const void* weight, int weight_is_fp32, int64_t N, int64_t K,
+                       int group_size, int32_t* packed_w, float* scales, int32_t* zeros,
+                       int device, void* stream);
+
 /* Reads (and clears) the device-side status word of `device`: 0, or a code left by a
  * kernel whose bounded wait on a barrier expired.  Synchronises the device. */
 int lbl_device_status(int device, int* status);

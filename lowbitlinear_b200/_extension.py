@@ -11,6 +11,7 @@ rather than a torch extension, so after loading it this module binds the entry p
 (``lowbitlinear_ext::w4a16_gemv_warp_vec`` and ``lowbitlinear_cute_w4a16::gemm``, CUDA
 dispatch key only) on top of them -- see ``_ops.py``.
 """
+import warnings
 from importlib.machinery import EXTENSION_SUFFIXES
 from pathlib import Path
 
@@ -18,6 +19,17 @@ import torch
 
 _loaded_library = None
 _native = None  # ctypes handle with typed entry points, set by load_cuda_extension
+
+
+def _is_out_of_date():
+    """True when this tree records a build whose sources differ from the present ones."""
+    from ._fingerprint import recorded_build, source_fingerprint
+
+    recorded = recorded_build()
+    if recorded is None:
+        return False
+    fingerprint, flags, defines = recorded
+    return source_fingerprint(flags, defines) != fingerprint
 
 
 def _candidate_libraries():
@@ -45,6 +57,15 @@ def load_cuda_extension(*, required=False):
     if len(libraries) != 1:
         raise ImportError(f"Ambiguous lowbitlinear_b200 native libraries: {libraries}")
     path = libraries[0]
+    if _is_out_of_date():
+        # Checked before the loader touches the file: a library that was loaded once stays
+        # mapped for the life of the process, even after a rebuild.
+        message = (f"{path} was built from older sources; rebuild it with: "
+                   "python -m lowbitlinear_b200.build")
+        if required:
+            raise ImportError(message)
+        warnings.warn(message, RuntimeWarning, stacklevel=2)
+        return False
     # Errors from the dynamic loader propagate: a CUDA installation with a broken library
     # must fail loudly.
     torch.ops.load_library(str(path))

@@ -78,6 +78,8 @@ def bind(path):
     lib.lbl_w4a16_gemv_allreduce.restype = i32
     lib.lbl_w4a16_gemv_allreduce.argtypes = [p, p, p, p, p, i64, i64, i32, i32, i32, ctypes.POINTER(p), i64,
                                              p, sz, u32, i32, p]
+    lib.lbl_w4a16_quantize.restype = i32
+    lib.lbl_w4a16_quantize.argtypes = [p, i32, i64, i64, i32, p, p, p, i32, p]
     _lib = lib
     return lib
 
@@ -253,6 +255,28 @@ def gemv_allreduce(x, packed_w, scales, zeros, exchange):
                                          exchange.world, exchange.pointers, exchange.capacity_n, ws,
                                          ws_bytes, _flags, x.device.index, stream))
     return y
+
+
+def quantize_pack(weight, group_size=64):
+    """quantize_int4 + pack_int4 of a CUDA weight in one kernel.  Returns (packed, scales, zeros)
+    in the reference layout, bit-identical to the reference's CPU result
+    (lowbitlinear/quantization.py:33-86, :112-141)."""
+    _require(weight.is_cuda, "weight must be a CUDA tensor")
+    _require(weight.dim() == 2, "weight must have shape [out_features, in_features]")
+    _require(weight.dtype in (torch.float16, torch.float32), "weight must be FP16 or FP32")
+    _require(group_size == 64, "the device quantiser supports group_size=64 only")
+    weight = weight.contiguous()
+    n, k = weight.shape
+    _require(k > 0, "in_features must be positive")
+    groups = (k + 63) // 64
+    packed = torch.empty((n, (k + 7) // 8), dtype=torch.int32, device=weight.device)
+    scales = torch.empty((n, groups), dtype=torch.float32, device=weight.device)
+    zeros = torch.empty((n, groups), dtype=torch.int32, device=weight.device)
+    stream = torch.cuda.current_stream(weight.device).cuda_stream
+    _check(_lib.lbl_w4a16_quantize(weight.data_ptr(), int(weight.dtype == torch.float32), n, k, group_size,
+                                   packed.data_ptr(), scales.data_ptr(), zeros.data_ptr(),
+                                   weight.device.index, stream))
+    return packed, scales, zeros
 
 
 def select_path(m, n, k, op=1):

@@ -8,7 +8,6 @@ for it.  nvcc cross-compiles, so no GPU is needed to build.
     python -m lowbitlinear_b200.build [--force] [--verbose] [-D NAME[=VALUE] ...]
 """
 import argparse
-import hashlib
 import os
 import shutil
 import subprocess
@@ -16,12 +15,15 @@ import sys
 from concurrent.futures import ThreadPoolExecutor
 from pathlib import Path
 
-PACKAGE_DIR = Path(__file__).resolve().parent
-CSRC = PACKAGE_DIR / "csrc"
-INCLUDE = PACKAGE_DIR.parent / "include"
+try:
+    from ._fingerprint import BUILD_DIR, CSRC, DEFINES, INCLUDE, PACKAGE_DIR, STAMP, source_fingerprint
+except ImportError:  # run as a plain script
+    sys.path.insert(0, str(Path(__file__).resolve().parent))
+    from _fingerprint import BUILD_DIR, CSRC, DEFINES, INCLUDE, PACKAGE_DIR, STAMP, source_fingerprint
+
 OUTPUT = PACKAGE_DIR / "_C.so"
-BUILD_DIR = PACKAGE_DIR / "build"
-SOURCES = ("api.cu", "generic.cu", "skinny.cu", "gemv_decode.cu", "gemm_tc.cu", "tensor_map.cu")
+SOURCES = ("api.cu", "generic.cu", "skinny.cu", "gemv_decode.cu", "gemm_tc.cu", "quantize.cu",
+           "tensor_map.cu")
 ARCH_FLAGS = ("-gencode", "arch=compute_100a,code=sm_100a")
 COMMON_FLAGS = ("-O3", "-std=c++17", "-lineinfo", "-Xcompiler", "-fPIC", "-Xptxas", "-v")
 
@@ -33,20 +35,11 @@ def find_nvcc():
     raise RuntimeError("nvcc not found; set NVCC or put it on PATH")
 
 
-def _fingerprint(defines):
-    digest = hashlib.sha256()
-    for path in sorted(list(CSRC.glob("*")) + list(INCLUDE.glob("*.h")) + [Path(__file__)]):
-        if path.is_file():
-            digest.update(path.name.encode())
-            digest.update(path.read_bytes())
-    digest.update(repr((ARCH_FLAGS, COMMON_FLAGS, tuple(defines))).encode())
-    return digest.hexdigest()
-
-
 def build(force=False, verbose=False, defines=()):
     """Compile and link ``_C.so``; returns its path.  Skips work when nothing changed."""
-    stamp = BUILD_DIR / "fingerprint"
-    fingerprint = _fingerprint(defines)
+    stamp = STAMP
+    flags = ARCH_FLAGS + COMMON_FLAGS
+    fingerprint = source_fingerprint(flags, defines)
     if not force and OUTPUT.is_file() and stamp.is_file() and stamp.read_text() == fingerprint:
         return OUTPUT
     nvcc = find_nvcc()
@@ -75,6 +68,7 @@ def build(force=False, verbose=False, defines=()):
     if result.returncode != 0:
         sys.stderr.write(result.stdout + result.stderr)
         raise RuntimeError("link failed")
+    DEFINES.write_text("\t".join(flags) + "\n" + "".join(f"{d}\n" for d in defines))
     stamp.write_text(fingerprint)
     return OUTPUT
 

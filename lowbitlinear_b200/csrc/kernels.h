@@ -23,6 +23,11 @@ struct Problem {
 // ----- masked any-shape kernel (generic.cu) ----------------------------------------------------
 cudaError_t launch_generic(const Problem& p, bool round_weights_to_fp16, cudaStream_t stream);
 
+// ----- quantiser + packer (quantize.cu) --------------------------------------------------------
+// weight [N, K] FP16 or FP32 -> packed [N, ceil(K/8)], scales / zeros [N, ceil(K/64)].
+cudaError_t launch_quantize(const void* weight, bool weight_is_fp32, int64_t N, int64_t K,
+                            uint32_t* packed, float* scales, int32_t* zeros, cudaStream_t stream);
+
 // ----- streaming skinny kernel, optional split-K (skinny.cu) -----------------------------------
 struct SkinnyPlan {
   int kseg;         // columns of K handled by one unit; divides K; multiple of 256

@@ -25,8 +25,7 @@ from .quantization import (
     _validate_matrix,
     _validate_metadata,
     dequantize_int4,
-    pack_int4,
-    quantize_int4,
+    quantize_pack_int4,
     unpack_int4,
 )
 
@@ -84,8 +83,7 @@ class QuantizedLinear(torch.nn.Module):
         if isinstance(bits, bool) or bits != 4:
             raise ValueError("Only bits=4 is supported")
         with torch.no_grad():
-            levels, scales, zeros = quantize_int4(weight, group_size)
-            packed = pack_int4(levels)
+            packed, scales, zeros = quantize_pack_int4(weight, group_size)
         return cls(packed, scales, zeros, group_size, in_features=weight.shape[1])
 
     def forward(self, x):

@@ -104,6 +104,27 @@ def quantize_int4(weight, group_size=64):
     return q, scales, zeros
 
 
+def quantize_pack_int4(weight, group_size=64):
+    """``quantize_int4`` followed by ``pack_int4``: ``(packed [N, ceil(K/8)] int32, scales, zeros)``.
+
+    A CUDA weight with ``group_size == 64`` goes through the library's one-pass quantiser kernel
+    when the native library is built; its results are bit-identical to this module's CPU
+    arithmetic (the torch CUDA ops may differ from the CPU in the last bit of a scale).  Every
+    other case runs the two torch functions.
+    """
+    _validate_matrix(weight, "weight", (torch.float16, torch.float32))
+    _validate_group_size(weight.shape[1], group_size)
+    if weight.is_cuda and group_size == 64:
+        from ._extension import load_cuda_extension
+
+        if load_cuda_extension(required=False):
+            from . import _ops
+
+            return _ops.quantize_pack(weight, group_size)
+    levels, scales, zeros = quantize_int4(weight, group_size)
+    return pack_int4(levels), scales, zeros
+
+
 def dequantize_int4(qweight, scales, zeros, group_size=64):
     """``(q - zero) * scale`` per group, FP32 ``[N, K]``."""
     _validate_matrix(qweight, "qweight", (torch.uint8,))
