@@ -11,6 +11,7 @@ rather than a torch extension, so after loading it this module binds the entry p
 (``lowbitlinear_ext::w4a16_gemv_warp_vec`` and ``lowbitlinear_cute_w4a16::gemm``, CUDA
 dispatch key only) on top of them -- see ``_ops.py``.
 """
+import sys
 import warnings
 from importlib.machinery import EXTENSION_SUFFIXES
 from pathlib import Path
@@ -64,7 +65,8 @@ def load_cuda_extension(*, required=False):
                    "python -m lowbitlinear_b200.build")
         if required:
             raise ImportError(message)
-        warnings.warn(message, RuntimeWarning, stacklevel=2)
+        if "lowbitlinear_b200.build" not in getattr(sys, "orig_argv", ()):  # not while rebuilding
+            warnings.warn(message, RuntimeWarning, stacklevel=2)
         return False
     # Errors from the dynamic loader propagate: a CUDA installation with a broken library
     # must fail loudly.

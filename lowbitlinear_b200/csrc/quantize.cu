@@ -8,9 +8,10 @@
 //   scale = (hi - lo) / 15       IEEE division; 1 when the quotient is not positive
 //   zero  = clamp(rint(-lo / scale), 0, 15)
 //   q     = clamp(rint(w / scale + zero), 0, 15)      division, then a separate addition
-// (round half to even, no fused multiply-add, no reciprocal).  One warp owns one group of one
-// row: a lane holds two neighbouring weights, min / max go through shuffles, two levels make a
-// byte and four lanes' bytes make a word.  Columns past K pack as level 0, as the reference pads.
+// (round half to even, no fused multiply-add, no reciprocal).  Sixteen lanes own one group of
+// one row: a lane holds four neighbouring weights, min / max go through shuffles, a lane's four
+// levels make half a word and two lanes make a word.  Columns past K pack as level 0, as the
+// reference pads.
 #include "kernels.h"
 
 namespace lbl {
@@ -18,63 +19,92 @@ namespace {
 
 constexpr int kWarpsPerCta = 8;
 
+// Four neighbouring weights of one row as floats; columns at or past `limit` read as 0.
 template <typename T>
-__device__ __forceinline__ float to_float(T v);
+__device__ __forceinline__ void load4(const T* row, int64_t k0, int64_t limit, bool vector_ok,
+                                      float (&w)[4]);
+
 template <>
-__device__ __forceinline__ float to_float<float>(float v) {
-  return v;
-}
-template <>
-__device__ __forceinline__ float to_float<__half>(__half v) {
-  return __half2float(v);
+__device__ __forceinline__ void load4<__half>(const __half* row, int64_t k0, int64_t limit,
+                                              bool vector_ok, float (&w)[4]) {
+  if (vector_ok && k0 + 4 <= limit) {
+    const uint2 raw = *reinterpret_cast<const uint2*>(row + k0);
+    const float2 a = __half22float2(*reinterpret_cast<const __half2*>(&raw.x));
+    const float2 b = __half22float2(*reinterpret_cast<const __half2*>(&raw.y));
+    w[0] = a.x, w[1] = a.y, w[2] = b.x, w[3] = b.y;
+  } else {
+#pragma unroll
+    for (int i = 0; i < 4; ++i) w[i] = (k0 + i < limit) ? __half2float(row[k0 + i]) : 0.0f;
+  }
 }
 
+template <>
+__device__ __forceinline__ void load4<float>(const float* row, int64_t k0, int64_t limit,
+                                             bool vector_ok, float (&w)[4]) {
+  if (vector_ok && k0 + 4 <= limit) {
+    const float4 raw = *reinterpret_cast<const float4*>(row + k0);
+    w[0] = raw.x, w[1] = raw.y, w[2] = raw.z, w[3] = raw.w;
+  } else {
+#pragma unroll
+    for (int i = 0; i < 4; ++i) w[i] = (k0 + i < limit) ? row[k0 + i] : 0.0f;
+  }
+}
+
+// A warp owns two neighbouring groups of one row (16 lanes each, four weights per lane).
 template <typename T>
 __global__ void __launch_bounds__(kWarpsPerCta * 32)
     w4_quantize_pack_kernel(const T* __restrict__ weight, uint32_t* __restrict__ packed,
                             float* __restrict__ scales, int32_t* __restrict__ zeros, int64_t N,
-                            int64_t K) {
+                            int64_t K, bool vector_ok) {
   const int lane = threadIdx.x & 31;
   const int64_t groups = (K + 63) / 64;
+  const int64_t pairs = (groups + 1) / 2;
   const int64_t words = (K + 7) / 8;
+  const int64_t total = N * pairs;
   const int64_t item = static_cast<int64_t>(blockIdx.x) * kWarpsPerCta + (threadIdx.x >> 5);
-  if (item >= N * groups) return;
-  const int64_t row = item / groups;
-  const int64_t group = item - row * groups;
-  const int64_t k0 = group * 64 + 2 * lane;
+  if (item >= total) return;
+  int64_t row, pair;
+  if (total <= 0xffffffffLL) {  // the usual case: one 32-bit division instead of a 64-bit one
+    const uint32_t r = static_cast<uint32_t>(item) / static_cast<uint32_t>(pairs);
+    row = r;
+    pair = static_cast<uint32_t>(item) - r * static_cast<uint32_t>(pairs);
+  } else {
+    row = item / pairs;
+    pair = item - row * pairs;
+  }
+  const int sub = lane & 15;
+  const int64_t group = pair * 2 + (lane >> 4);
+  const bool group_ok = group < groups;
+  const int64_t k0 = group * 64 + 4 * sub;
 
-  const bool in0 = k0 < K;
-  const bool in1 = k0 + 1 < K;
-  const T* src = weight + row * K + k0;
-  const float w0 = in0 ? to_float<T>(src[0]) : 0.0f;
-  const float w1 = in1 ? to_float<T>(src[1]) : 0.0f;
+  float w[4];
+  load4<T>(weight + row * K, k0, group_ok ? K : 0, vector_ok, w);
 
   // Zeros for the missing columns leave a minimum clamped to <= 0 and a maximum clamped to >= 0
   // unchanged.
-  float lo = fminf(fminf(w0, w1), 0.0f);
-  float hi = fmaxf(fmaxf(w0, w1), 0.0f);
+  float lo = fminf(fminf(fminf(w[0], w[1]), fminf(w[2], w[3])), 0.0f);
+  float hi = fmaxf(fmaxf(fmaxf(w[0], w[1]), fmaxf(w[2], w[3])), 0.0f);
 #pragma unroll
-  for (int offset = 16; offset > 0; offset >>= 1) {
+  for (int offset = 8; offset > 0; offset >>= 1) {  // stays inside each half of the warp
     lo = fminf(lo, __shfl_xor_sync(0xffffffffu, lo, offset));
     hi = fmaxf(hi, __shfl_xor_sync(0xffffffffu, hi, offset));
   }
   const float raw = __fdiv_rn(__fsub_rn(hi, lo), 15.0f);
   const float scale = raw > 0.0f ? raw : 1.0f;
   const float zero_f = fminf(fmaxf(rintf(__fdiv_rn(-lo, scale)), 0.0f), 15.0f);
-  const float q0 = fminf(fmaxf(rintf(__fadd_rn(__fdiv_rn(w0, scale), zero_f)), 0.0f), 15.0f);
-  const float q1 = fminf(fmaxf(rintf(__fadd_rn(__fdiv_rn(w1, scale), zero_f)), 0.0f), 15.0f);
-  const uint32_t level0 = in0 ? static_cast<uint32_t>(q0) : 0u;
-  const uint32_t level1 = in1 ? static_cast<uint32_t>(q1) : 0u;
 
-  // byte = two levels, low nibble first; word = the bytes of four neighbouring lanes.
-  const uint32_t byte = level0 | (level1 << 4);
-  uint32_t word = byte;
-  word |= __shfl_down_sync(0xffffffffu, byte, 1) << 8;
-  word |= __shfl_down_sync(0xffffffffu, byte, 2) << 16;
-  word |= __shfl_down_sync(0xffffffffu, byte, 3) << 24;
-  const int64_t word_index = group * 8 + (lane >> 2);
-  if ((lane & 3) == 0 && word_index < words) packed[row * words + word_index] = word;
-  if (lane == 0) {
+  // Two levels make a byte (low nibble first), a lane's four levels make half a word.
+  uint32_t half_word = 0;
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    const float q = fminf(fmaxf(rintf(__fadd_rn(__fdiv_rn(w[i], scale), zero_f)), 0.0f), 15.0f);
+    const uint32_t level = (k0 + i < K) ? static_cast<uint32_t>(q) : 0u;
+    half_word |= level << (4 * i);
+  }
+  const uint32_t word = half_word | (__shfl_down_sync(0xffffffffu, half_word, 1) << 16);
+  const int64_t word_index = group * 8 + (sub >> 1);
+  if (group_ok && (sub & 1) == 0 && word_index < words) packed[row * words + word_index] = word;
+  if (group_ok && sub == 0) {
     scales[row * groups + group] = scale;
     zeros[row * groups + group] = static_cast<int32_t>(zero_f);
   }
@@ -85,16 +115,19 @@ __global__ void __launch_bounds__(kWarpsPerCta * 32)
 cudaError_t launch_quantize(const void* weight, bool weight_is_fp32, int64_t N, int64_t K,
                             uint32_t* packed, float* scales, int32_t* zeros, cudaStream_t stream) {
   const int64_t groups = (K + 63) / 64;
-  const int64_t items = N * groups;
+  const int64_t items = N * ((groups + 1) / 2);
   const int64_t blocks = (items + kWarpsPerCta - 1) / kWarpsPerCta;
   if (blocks <= 0 || blocks > 0x7fffffffLL) return cudaErrorInvalidConfiguration;
   const dim3 grid(static_cast<unsigned>(blocks));
+  // 8- or 16-byte loads need every row to start on such a boundary.
+  const size_t vector_bytes = weight_is_fp32 ? 16 : 8;
+  const bool vector_ok = K % 4 == 0 && reinterpret_cast<uintptr_t>(weight) % vector_bytes == 0;
   if (weight_is_fp32) {
     w4_quantize_pack_kernel<float><<<grid, kWarpsPerCta * 32, 0, stream>>>(
-        static_cast<const float*>(weight), packed, scales, zeros, N, K);
+        static_cast<const float*>(weight), packed, scales, zeros, N, K, vector_ok);
   } else {
     w4_quantize_pack_kernel<__half><<<grid, kWarpsPerCta * 32, 0, stream>>>(
-        static_cast<const __half*>(weight), packed, scales, zeros, N, K);
+        static_cast<const __half*>(weight), packed, scales, zeros, N, K, vector_ok);
   }
   return cudaGetLastError();
 }
