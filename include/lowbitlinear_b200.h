@@ -157,6 +157,15 @@ int lbl_w4a16_quantize(const void* weight, int weight_is_fp32, int64_t N, int64_
                        int group_size, int32_t* packed_w, float* scales, int32_t* zeros,
                        int device, void* stream);
 
+/* The inverse for weights on the GPU: unpack_int4 + dequantize_int4
+ * (lowbitlinear/quantization.py:143-171 and :88-110) in one kernel.  Writes weight [N, K] =
+ * float(q - zero) * scale, as FP32 (weight_is_fp32 != 0, bit-identical to the reference) or
+ * rounded once to FP16 (the dense matrix the reference benchmark's pre-dequantised baseline
+ * multiplies, benchmarks/bench_w4a16.py:37-43).  group_size must be 64. */
+int lbl_w4a16_dequantize(const int32_t* packed_w, const float* scales, const int32_t* zeros,
+                         void* weight, int weight_is_fp32, int64_t N, int64_t K, int group_size,
+                         int device, void* stream);
+
 /* Reads (and clears) the device-side status word of `device`: 0, or a code left by a
  * kernel whose bounded wait on a barrier expired.  Synchronises the device. */
 int lbl_device_status(int device, int* status);

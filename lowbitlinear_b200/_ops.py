@@ -80,6 +80,8 @@ def bind(path):
                                              p, sz, u32, i32, p]
     lib.lbl_w4a16_quantize.restype = i32
     lib.lbl_w4a16_quantize.argtypes = [p, i32, i64, i64, i32, p, p, p, i32, p]
+    lib.lbl_w4a16_dequantize.restype = i32
+    lib.lbl_w4a16_dequantize.argtypes = [p, p, p, p, i32, i64, i64, i32, i32, p]
     _lib = lib
     return lib
 
@@ -277,6 +279,32 @@ def quantize_pack(weight, group_size=64):
                                    packed.data_ptr(), scales.data_ptr(), zeros.data_ptr(),
                                    weight.device.index, stream))
     return packed, scales, zeros
+
+
+def dequantize(packed_w, scales, zeros, in_features=None, dtype=torch.float16, group_size=64):
+    """unpack_int4 + dequantize_int4 of CUDA buffers in one kernel: the dense ``[N, K]`` weight
+    ``float(q - zero) * scale`` as FP32 (bit-identical to ``lowbitlinear/quantization.py:88-110``)
+    or rounded once to FP16."""
+    _require(packed_w.is_cuda and scales.is_cuda and zeros.is_cuda, "buffers must be CUDA tensors")
+    _require(packed_w.dtype == torch.int32 and packed_w.dim() == 2, "packed_w must be a 2-D INT32 tensor")
+    _require(dtype in (torch.float16, torch.float32), "dtype must be FP16 or FP32")
+    _require(group_size == 64, "the device dequantiser supports group_size=64 only")
+    n, words = packed_w.shape
+    k = words * 8 if in_features is None else int(in_features)
+    _require(0 < k <= words * 8 and (k + 7) // 8 == words, "in_features does not match packed_w")
+    groups = (k + 63) // 64
+    _require(scales.dtype == torch.float32 and tuple(scales.shape) == (n, groups), "Invalid scales or zeros shape")
+    _require(zeros.dtype == torch.int32 and tuple(zeros.shape) == (n, groups), "Invalid scales or zeros shape")
+    _require(packed_w.is_contiguous() and scales.is_contiguous() and zeros.is_contiguous(),
+             "buffers must be contiguous")
+    _require(scales.device == packed_w.device and zeros.device == packed_w.device,
+             "All tensors must be on the same device")
+    weight = torch.empty((n, k), dtype=dtype, device=packed_w.device)
+    stream = torch.cuda.current_stream(packed_w.device).cuda_stream
+    _check(_lib.lbl_w4a16_dequantize(packed_w.data_ptr(), scales.data_ptr(), zeros.data_ptr(),
+                                     weight.data_ptr(), int(dtype == torch.float32), n, k, group_size,
+                                     packed_w.device.index, stream))
+    return weight
 
 
 def select_path(m, n, k, op=1):

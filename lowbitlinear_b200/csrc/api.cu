@@ -316,6 +316,26 @@ int lbl_w4a16_quantize(const void* weight, int weight_is_fp32, int64_t N, int64_
   return LBL_OK;
 }
 
+int lbl_w4a16_dequantize(const int32_t* packed_w, const float* scales, const int32_t* zeros,
+                         void* weight, int weight_is_fp32, int64_t N, int64_t K, int group_size,
+                         int device, void* stream) {
+  if (group_size != 64) {
+    return fail(LBL_ERR_UNSUPPORTED, "the device dequantiser supports group_size=64 only (got %d)", group_size);
+  }
+  if (N < 0 || K <= 0) return fail(LBL_ERR_INVALID, "Invalid N or K (N=%lld K=%lld)", (long long)N, (long long)K);
+  if (N == 0) return LBL_OK;
+  if (weight == nullptr || packed_w == nullptr || scales == nullptr || zeros == nullptr) {
+    return fail(LBL_ERR_INVALID, "null tensor pointer");
+  }
+  DeviceScope scope(device);
+  if (!scope.ok()) return fail(LBL_ERR_CUDA, "cannot make device %d current", device);
+  const cudaError_t err = lbl::launch_dequantize(reinterpret_cast<const uint32_t*>(packed_w), scales,
+                                                 zeros, weight, weight_is_fp32 != 0, N, K,
+                                                 static_cast<cudaStream_t>(stream));
+  if (err != cudaSuccess) return fail_cuda(err, "dequantise launch");
+  return LBL_OK;
+}
+
 int lbl_device_status(int device, int* status) {
   if (status == nullptr) return fail(LBL_ERR_INVALID, "status is null");
   DeviceScope scope(device);

@@ -28,6 +28,11 @@ cudaError_t launch_generic(const Problem& p, bool round_weights_to_fp16, cudaStr
 cudaError_t launch_quantize(const void* weight, bool weight_is_fp32, int64_t N, int64_t K,
                             uint32_t* packed, float* scales, int32_t* zeros, cudaStream_t stream);
 
+// packed [N, ceil(K/8)] + scales / zeros -> dense weight [N, K], FP16 or FP32.
+cudaError_t launch_dequantize(const uint32_t* packed, const float* scales, const int32_t* zeros,
+                              void* out, bool out_is_fp32, int64_t N, int64_t K,
+                              cudaStream_t stream);
+
 // ----- streaming skinny kernel, optional split-K (skinny.cu) -----------------------------------
 struct SkinnyPlan {
   int kseg;         // columns of K handled by one unit; divides K; multiple of 256

@@ -110,6 +110,58 @@ __global__ void __launch_bounds__(kWarpsPerCta * 32)
   }
 }
 
+// ---------------------------------------------------------------------------------------------
+// Dequantiser: packed words -> dense weights, w = float(q - zero) * scale in FP32
+// (lowbitlinear/quantization.py:88-110 after :143-171), stored as FP32 or rounded once to FP16
+// (what the reference benchmark's pre-dequantised baseline holds, bench_w4a16.py:37-43).
+// A thread expands one word into eight neighbouring weights; HBM-bound on its own stores.
+// ---------------------------------------------------------------------------------------------
+template <typename Out>
+__global__ void __launch_bounds__(256)
+    w4_dequantize_kernel(const uint32_t* __restrict__ packed, const float* __restrict__ scales,
+                         const int32_t* __restrict__ zeros, Out* __restrict__ out, int64_t N,
+                         int64_t K, bool vector_ok) {
+  const int64_t words = (K + 7) / 8;
+  const int64_t groups = (K + 63) / 64;
+  const int64_t word = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x;
+  const int64_t row = blockIdx.y;
+  if (word >= words) return;
+  const uint32_t bits = packed[row * words + word];
+  const float scale = scales[row * groups + (word >> 3)];
+  const int zero = zeros[row * groups + (word >> 3)];
+  float w[8];
+#pragma unroll
+  for (int i = 0; i < 8; ++i) {
+    w[i] = __fmul_rn(static_cast<float>(static_cast<int>((bits >> (4 * i)) & 15u) - zero), scale);
+  }
+  Out* dst = out + row * K + word * 8;
+  if (vector_ok) {  // K % 8 == 0 and an aligned base: every thread owns 16 or 32 aligned bytes
+    if constexpr (sizeof(Out) == 2) {
+      uint4 v;
+      __half2 h;
+      h = __floats2half2_rn(w[0], w[1]), v.x = *reinterpret_cast<uint32_t*>(&h);
+      h = __floats2half2_rn(w[2], w[3]), v.y = *reinterpret_cast<uint32_t*>(&h);
+      h = __floats2half2_rn(w[4], w[5]), v.z = *reinterpret_cast<uint32_t*>(&h);
+      h = __floats2half2_rn(w[6], w[7]), v.w = *reinterpret_cast<uint32_t*>(&h);
+      *reinterpret_cast<uint4*>(dst) = v;
+    } else {
+      reinterpret_cast<float4*>(dst)[0] = make_float4(w[0], w[1], w[2], w[3]);
+      reinterpret_cast<float4*>(dst)[1] = make_float4(w[4], w[5], w[6], w[7]);
+    }
+  } else {
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+      if (word * 8 + i < K) {
+        if constexpr (sizeof(Out) == 2) {
+          dst[i] = __float2half_rn(w[i]);
+        } else {
+          dst[i] = w[i];
+        }
+      }
+    }
+  }
+}
+
 }  // namespace
 
 cudaError_t launch_quantize(const void* weight, bool weight_is_fp32, int64_t N, int64_t K,
@@ -130,6 +182,33 @@ cudaError_t launch_quantize(const void* weight, bool weight_is_fp32, int64_t N, 
         static_cast<const __half*>(weight), packed, scales, zeros, N, K, vector_ok);
   }
   return cudaGetLastError();
+}
+
+cudaError_t launch_dequantize(const uint32_t* packed, const float* scales, const int32_t* zeros,
+                              void* out, bool out_is_fp32, int64_t N, int64_t K,
+                              cudaStream_t stream) {
+  const int64_t words = (K + 7) / 8;
+  const int64_t groups = (K + 63) / 64;
+  const int64_t blocks_x = (words + 255) / 256;
+  if (N <= 0 || blocks_x > 0x7fffffffLL) return cudaErrorInvalidConfiguration;
+  const bool vector_ok = K % 8 == 0 && reinterpret_cast<uintptr_t>(out) % 16 == 0;
+  constexpr int64_t kRowsPerLaunch = 65535;  // limit of the grid's y extent
+  for (int64_t r0 = 0; r0 < N; r0 += kRowsPerLaunch) {
+    const int64_t rows = N - r0 < kRowsPerLaunch ? N - r0 : kRowsPerLaunch;
+    const dim3 grid(static_cast<unsigned>(blocks_x), static_cast<unsigned>(rows));
+    if (out_is_fp32) {
+      w4_dequantize_kernel<float><<<grid, 256, 0, stream>>>(
+          packed + r0 * words, scales + r0 * groups, zeros + r0 * groups,
+          static_cast<float*>(out) + r0 * K, rows, K, vector_ok);
+    } else {
+      w4_dequantize_kernel<__half><<<grid, 256, 0, stream>>>(
+          packed + r0 * words, scales + r0 * groups, zeros + r0 * groups,
+          static_cast<__half*>(out) + r0 * K, rows, K, vector_ok);
+    }
+    const cudaError_t err = cudaGetLastError();
+    if (err != cudaSuccess) return err;
+  }
+  return cudaSuccess;
 }
 
 }  // namespace lbl

@@ -140,3 +140,75 @@ def test_non_contiguous_and_other_group_sizes(cuda_ops):
     assert layer.scales.shape == (12, 8)
     with pytest.raises(RuntimeError, match="group_size=64"):
         _ops.quantize_pack(torch.from_numpy(wide).to(cuda_ops), 32)
+
+
+# ---- device dequantiser (lbl_w4a16_dequantize) ------------------------------------------------
+
+def _device_dequantize(packed, scales, zeros, k, dtype, device):
+    from lowbitlinear_b200 import _ops
+
+    out = _ops.dequantize(*(torch.from_numpy(a).to(device) for a in (packed, scales, zeros)),
+                          in_features=k, dtype=dtype)
+    torch.cuda.synchronize(device)
+    return out.cpu().numpy()
+
+
+@pytest.mark.parametrize("n,k", [(1, 1), (3, 7), (5, 8), (4, 64), (5, 65), (7, 100), (33, 1000),
+                                 (128, 4096), (17, 4104)])
+def test_dequantize_matches_oracle(cuda_ops, n, k):
+    rng = np.random.default_rng(2000 * n + k)
+    weight = (rng.standard_normal((n, k), dtype=np.float32) * np.float32(0.02)).astype(np.float16)
+    q, scales, zeros = oracle.quantize_int4(weight, 64)
+    packed = oracle.pack_int4(q)
+    expected = oracle.dequantize_int4(oracle.unpack_int4(packed, original_k=k), scales, zeros, 64)
+    as_fp32 = _device_dequantize(packed, scales, zeros, k, torch.float32, cuda_ops)
+    assert as_fp32.shape == (n, k)
+    assert np.array_equal(as_fp32.view(np.uint32), expected.view(np.uint32))
+    as_fp16 = _device_dequantize(packed, scales, zeros, k, torch.float16, cuda_ops)
+    assert np.array_equal(as_fp16.view(np.uint16), expected.astype(np.float16).view(np.uint16))
+
+
+def test_dequantize_reference_fixtures(cuda_ops, golden_small):
+    for name, case in golden_small.items():
+        if int(case["group_size"]) != 64:
+            continue
+        k = case["weight"].shape[1]
+        expected = oracle.dequantize_int4(case["q"], case["scales"], case["zeros"], 64)
+        got = _device_dequantize(case["packed"], case["scales"], case["zeros"], k, torch.float32, cuda_ops)
+        assert np.array_equal(got.view(np.uint32), expected.view(np.uint32)), name
+
+
+def test_dequantize_every_level_and_zero_point(cuda_ops):
+    """All 16 x 16 combinations of level and zero point under an awkward scale."""
+    levels = np.tile(np.arange(16, dtype=np.uint8), 4)[None].repeat(16, 0)        # [16, 64]
+    zeros = np.arange(16, dtype=np.int32)[:, None]
+    scales = np.full((16, 1), 0.0123456789, np.float32)
+    packed = oracle.pack_int4(levels)
+    got = _device_dequantize(packed, scales, zeros, 64, torch.float32, cuda_ops)
+    expected = oracle.dequantize_int4(levels, scales, zeros, 64)
+    assert np.array_equal(got.view(np.uint32), expected.view(np.uint32))
+
+
+def test_round_trip_at_benchmark_size(cuda_ops):
+    """Size-independent properties on a 4096 x 12288 linear, without the CPU: the device
+    dequantiser equals the package's torch arithmetic on the same buffers bit for bit, the
+    reconstruction error stays within one quantisation step (half from rounding the level, half
+    from rounding the zero point), and the dense FP16 matrix
+    multiplied by x agrees with the GEMV kernel on the packed form."""
+    from lowbitlinear_b200 import _ops
+    from lowbitlinear_b200.quantization import dequantize_int4, unpack_int4
+
+    g = torch.Generator("cpu").manual_seed(21)
+    weight = (torch.randn(4096, 12288, generator=g) * 0.02).half().to(cuda_ops)
+    x = torch.randn(1, 12288, generator=g).half().to(cuda_ops)
+    packed, scales, zeros = _ops.quantize_pack(weight)
+    dense = _ops.dequantize(packed, scales, zeros, dtype=torch.float32)
+    assert torch.equal(dense, dequantize_int4(unpack_int4(packed), scales, zeros, 64))
+    error = (dense - weight.float()).abs()
+    bound = scales.repeat_interleave(64, dim=1) * (1 + 1e-5)
+    assert bool((error <= bound).all()), "reconstruction error exceeds one step"
+    dense_fp16 = _ops.dequantize(packed, scales, zeros, dtype=torch.float16)
+    assert torch.equal(dense_fp16, dense.half())
+    y = _ops.w4a16_gemv_warp_vec(x, packed, scales, zeros, 64).float()
+    expected = x.float() @ dense.t()
+    torch.testing.assert_close(y, expected, atol=1e-2, rtol=1e-2)
