@@ -33,6 +33,7 @@ GEMM_SCHEMA = "gemm(Tensor X, Tensor packed_w, Tensor scales, Tensor zeros) -> T
 
 _lib = None
 _registered = []  # keeps the torch.library.Library objects alive
+ERR_WORKSPACE = -3  # LBL_ERR_WORKSPACE
 _flags = 0
 _workspaces = {}
 _workspace_lock = threading.Lock()
@@ -96,24 +97,44 @@ def set_programmatic_dependent_launch(enabled):
     _flags = (_flags | FLAG_PDL) if enabled else (_flags & ~FLAG_PDL)
 
 
+def _raw_stream(device):
+    """Handle of the current stream of ``device`` (what ``torch.cuda.current_stream(device)
+    .cuda_stream`` returns, without building the Python stream object)."""
+    return torch._C._cuda_getCurrentRawStream(device.index)
+
+
 def _check(rc):
     if rc != 0:
         raise RuntimeError(_lib.lbl_last_error().decode() or f"lowbitlinear_b200 error {rc}")
 
 
-def _workspace(device, stream, m, n, k, path=PATH_AUTO):
+def _workspace(device, stream, m, n, k, path=PATH_AUTO, exact=False):
     """Scratch for split-K, cached per (device, stream): zeroed when created, and every kernel
-    leaves its counters zero again."""
-    need = _lib.lbl_w4a16_workspace_bytes(m, n, k, path)
-    if need == 0:
-        return None, 0
+    leaves its counters zero again.  Returns ``(pointer, bytes)``.
+
+    The usual call hands out the cached buffer without asking the library how much this problem
+    needs (1 MiB covers the common shapes); ``exact=True`` asks, and grows the buffer if needed."""
     key = (device.index, stream)
+    entry = _workspaces.get(key)
+    if entry is not None and not exact:
+        return entry[1], entry[2]
+    need = max(_lib.lbl_w4a16_workspace_bytes(m, n, k, path), 1 << 20)
     with _workspace_lock:
-        buf = _workspaces.get(key)
-        if buf is None or buf.numel() < need:
-            buf = torch.zeros(max(need, 1 << 20), dtype=torch.uint8, device=device)
-            _workspaces[key] = buf
-    return buf.data_ptr(), buf.numel()
+        entry = _workspaces.get(key)
+        if entry is None or entry[2] < need:
+            buf = torch.zeros(need, dtype=torch.uint8, device=device)
+            entry = (buf, buf.data_ptr(), need)
+            _workspaces[key] = entry
+    return entry[1], entry[2]
+
+
+def _run(device, stream, m, n, k, path, call):
+    """``call(ws, ws_bytes) -> rc`` with the cached scratch; if the library finds it too small,
+    once more with a buffer of the size it asks for (nothing was launched by the first try)."""
+    rc = call(*_workspace(device, stream, m, n, k, path))
+    if rc == ERR_WORKSPACE:
+        rc = call(*_workspace(device, stream, m, n, k, path, exact=True))
+    _check(rc)
 
 
 def device_status(device=None):
@@ -163,11 +184,12 @@ def w4a16_gemv_warp_vec(x, packed_w, scales, zeros, group_size):
     _require(x.data_ptr() % 16 == 0, "x must be 16-byte aligned for vector loads")
 
     y = torch.empty((1, n), dtype=torch.float16, device=x.device)
-    stream = torch.cuda.current_stream(x.device).cuda_stream
-    ws, ws_bytes = _workspace(x.device, stream, 1, n, k)
-    _check(_lib.lbl_w4a16_gemv(x.data_ptr(), packed_w.data_ptr(), scales.data_ptr(),
-                               zeros.data_ptr(), y.data_ptr(), n, k, group_size, ws, ws_bytes,
-                               _flags, x.device.index, stream))
+    stream = _raw_stream(x.device)
+    px, pw, ps, pz, py, index = (x.data_ptr(), packed_w.data_ptr(), scales.data_ptr(), zeros.data_ptr(),
+                                 y.data_ptr(), x.device.index)
+    _run(x.device, stream, 1, n, k, PATH_AUTO,
+         lambda ws, ws_bytes: _lib.lbl_w4a16_gemv(px, pw, ps, pz, py, n, k, group_size, ws, ws_bytes,
+                                                  _flags, index, stream))
     return y
 
 
@@ -204,11 +226,12 @@ def w4a16_gemm(X, packed_w, scales, zeros):
     Y = torch.empty((m, n), dtype=torch.float16, device=X.device)
     if m == 0 or n == 0:
         return Y
-    stream = torch.cuda.current_stream(X.device).cuda_stream
-    ws, ws_bytes = _workspace(X.device, stream, m, n, k) if k > 0 else (None, 0)
-    _check(_lib.lbl_w4a16_gemm(X.data_ptr(), packed_w.data_ptr(), scales.data_ptr(),
-                               zeros.data_ptr(), Y.data_ptr(), m, n, k, ws, ws_bytes, _flags,
-                               X.device.index, stream))
+    stream = _raw_stream(X.device)
+    px, pw, ps, pz, py, index = (X.data_ptr(), packed_w.data_ptr(), scales.data_ptr(), zeros.data_ptr(),
+                                 Y.data_ptr(), X.device.index)
+    _run(X.device, stream, m, n, k, PATH_AUTO,
+         lambda ws, ws_bytes: _lib.lbl_w4a16_gemm(px, pw, ps, pz, py, m, n, k, ws, ws_bytes, _flags,
+                                                  index, stream))
     return Y
 
 
@@ -218,13 +241,13 @@ def linear_forced(X, packed_w, scales, zeros, path, op=1, flags=None):
     m, k = X.shape
     n = packed_w.size(0)
     Y = torch.empty((m, n), dtype=torch.float16, device=X.device)
-    stream = torch.cuda.current_stream(X.device).cuda_stream
-    ws, ws_bytes = _workspace(X.device, stream, m, n, k, path)
+    stream = _raw_stream(X.device)
     taken = ctypes.c_int(0)
-    _check(_lib.lbl_w4a16_linear(X.data_ptr(), packed_w.data_ptr(), scales.data_ptr(),
-                                 zeros.data_ptr(), Y.data_ptr(), m, n, k, op, path, ws, ws_bytes,
-                                 _flags if flags is None else flags, X.device.index, stream,
-                                 ctypes.byref(taken)))
+    _run(X.device, stream, m, n, k, path,
+         lambda ws, ws_bytes: _lib.lbl_w4a16_linear(
+             X.data_ptr(), packed_w.data_ptr(), scales.data_ptr(), zeros.data_ptr(), Y.data_ptr(),
+             m, n, k, op, path, ws, ws_bytes, _flags if flags is None else flags, X.device.index,
+             stream, ctypes.byref(taken)))
     return Y, taken.value
 
 
@@ -236,11 +259,12 @@ def linear_out(X, packed_w, scales, zeros, out, op=None):
     n = packed_w.size(0)
     if op is None:
         op = 0 if (m == 1 and k % 64 == 0 and n % 128 == 0) else 1
-    stream = torch.cuda.current_stream(X.device).cuda_stream
-    ws, ws_bytes = _workspace(X.device, stream, m, n, k)
-    _check(_lib.lbl_w4a16_linear(X.data_ptr(), packed_w.data_ptr(), scales.data_ptr(),
-                                 zeros.data_ptr(), out.data_ptr(), m, n, k, op, PATH_AUTO, ws, ws_bytes,
-                                 _flags, X.device.index, stream, None))
+    stream = _raw_stream(X.device)
+    px, pw, ps, pz, py, index = (X.data_ptr(), packed_w.data_ptr(), scales.data_ptr(), zeros.data_ptr(),
+                                 out.data_ptr(), X.device.index)
+    _run(X.device, stream, m, n, k, PATH_AUTO,
+         lambda ws, ws_bytes: _lib.lbl_w4a16_linear(px, pw, ps, pz, py, m, n, k, op, PATH_AUTO, ws,
+                                                    ws_bytes, _flags, index, stream, None))
     return out
 
 
@@ -250,12 +274,12 @@ def gemv_allreduce(x, packed_w, scales, zeros, exchange):
     ``exchange`` is a ``tensor_parallel.PeerExchange``."""
     n, k = packed_w.size(0), x.size(1)
     y = torch.empty((1, n), dtype=torch.float16, device=x.device)
-    stream = torch.cuda.current_stream(x.device).cuda_stream
-    ws, ws_bytes = _workspace(x.device, stream, 1, n, k)
-    _check(_lib.lbl_w4a16_gemv_allreduce(x.data_ptr(), packed_w.data_ptr(), scales.data_ptr(),
-                                         zeros.data_ptr(), y.data_ptr(), n, k, 64, exchange.rank,
-                                         exchange.world, exchange.pointers, exchange.capacity_n, ws,
-                                         ws_bytes, _flags, x.device.index, stream))
+    stream = _raw_stream(x.device)
+    _run(x.device, stream, 1, n, k, PATH_AUTO,
+         lambda ws, ws_bytes: _lib.lbl_w4a16_gemv_allreduce(
+             x.data_ptr(), packed_w.data_ptr(), scales.data_ptr(), zeros.data_ptr(), y.data_ptr(), n, k,
+             64, exchange.rank, exchange.world, exchange.pointers, exchange.capacity_n, ws, ws_bytes,
+             _flags, x.device.index, stream))
     return y
 
 
@@ -274,7 +298,7 @@ def quantize_pack(weight, group_size=64):
     packed = torch.empty((n, (k + 7) // 8), dtype=torch.int32, device=weight.device)
     scales = torch.empty((n, groups), dtype=torch.float32, device=weight.device)
     zeros = torch.empty((n, groups), dtype=torch.int32, device=weight.device)
-    stream = torch.cuda.current_stream(weight.device).cuda_stream
+    stream = _raw_stream(weight.device)
     _check(_lib.lbl_w4a16_quantize(weight.data_ptr(), int(weight.dtype == torch.float32), n, k, group_size,
                                    packed.data_ptr(), scales.data_ptr(), zeros.data_ptr(),
                                    weight.device.index, stream))
@@ -300,7 +324,7 @@ def dequantize(packed_w, scales, zeros, in_features=None, dtype=torch.float16, g
     _require(scales.device == packed_w.device and zeros.device == packed_w.device,
              "All tensors must be on the same device")
     weight = torch.empty((n, k), dtype=dtype, device=packed_w.device)
-    stream = torch.cuda.current_stream(packed_w.device).cuda_stream
+    stream = _raw_stream(packed_w.device)
     _check(_lib.lbl_w4a16_dequantize(packed_w.data_ptr(), scales.data_ptr(), zeros.data_ptr(),
                                      weight.data_ptr(), int(dtype == torch.float32), n, k, group_size,
                                      packed_w.device.index, stream))

@@ -508,7 +508,7 @@ bool skinny_make_plan(int64_t M, int64_t N, int64_t K, int want_split, int sm_co
 // takes 16 rows of one stage plus a few elements of padding per row.  The padding is outside the
 // inner extent, so it is zero-filled and costs no traffic, and it gives the rows in shared memory
 // the pitch that keeps the fragment loads free of bank conflicts.
-bool skinny_encode_maps(const Problem& p, const SkinnyPlan& plan, CUtensorMap* maps) {
+static bool encode_maps_uncached(const Problem& p, const SkinnyPlan& plan, CUtensorMap* maps) {
   const uint64_t stages_in_row = static_cast<uint64_t>(p.K / plan.stage_k);
   const uint64_t n_rows = static_cast<uint64_t>(p.N);
   {
@@ -529,6 +529,37 @@ bool skinny_encode_maps(const Problem& p, const SkinnyPlan& plan, CUtensorMap* m
                            CU_TENSOR_MAP_SWIZZLE_NONE) &&
          encode_tensor_map(&maps[2], CU_TENSOR_MAP_DATA_TYPE_INT32, 3, p.zeros, dims, strides, box,
                            CU_TENSOR_MAP_SWIZZLE_NONE);
+}
+
+// A tensor map is a pure function of the addresses, the shape and the box, and inference calls
+// the same few linears over and over: the last maps of each host thread are kept and reused,
+// which saves three driver calls per launch.
+bool skinny_encode_maps(const Problem& p, const SkinnyPlan& plan, CUtensorMap* maps) {
+  struct Entry {
+    const void* packed = nullptr;
+    const void* scales = nullptr;
+    const void* zeros = nullptr;
+    int64_t N = 0, K = 0;
+    int stage_k = 0, packed_pad = 0;
+    CUtensorMap maps[3];
+  };
+  constexpr int kEntries = 64;
+  thread_local Entry cache[kEntries];
+  const uintptr_t mix = reinterpret_cast<uintptr_t>(p.packed) >> 8;
+  Entry& e = cache[(mix ^ (mix >> 6) ^ (mix >> 12)) % kEntries];
+  const bool hit = e.packed == p.packed && e.scales == p.scales && e.zeros == p.zeros &&
+                   e.N == p.N && e.K == p.K && e.stage_k == plan.stage_k &&
+                   e.packed_pad == plan.packed_pad;
+  if (!hit) {
+    if (!encode_maps_uncached(p, plan, e.maps)) {
+      e.packed = nullptr;
+      return false;
+    }
+    e.packed = p.packed, e.scales = p.scales, e.zeros = p.zeros;
+    e.N = p.N, e.K = p.K, e.stage_k = plan.stage_k, e.packed_pad = plan.packed_pad;
+  }
+  for (int i = 0; i < 3; ++i) maps[i] = e.maps[i];
+  return true;
 }
 
 cudaError_t launch_skinny(const Problem& p, const SkinnyPlan& plan, float* partials, int* tickets,

@@ -86,25 +86,40 @@ class QuantizedLinear(torch.nn.Module):
             packed, scales, zeros = quantize_pack_int4(weight, group_size)
         return cls(packed, scales, zeros, group_size, in_features=weight.shape[1])
 
-    def forward(self, x):
-        _validate_packed_weight(
-            self.packed_weight, self.scales, self.zeros, self.group_size, self.in_features
+    def _state_key(self, packed_weight, scales, zeros):
+        """Everything ``_validate_packed_weight`` looks at: types, shapes, dtypes, devices and the
+        two integers.  Equal keys mean an equal verdict, so a key that passed once need not be
+        checked again; replacing or reshaping a buffer changes the key."""
+        return (
+            type(packed_weight), packed_weight.shape, packed_weight.dtype, packed_weight.device,
+            type(scales), scales.shape, scales.dtype, scales.device,
+            type(zeros), zeros.shape, zeros.dtype, zeros.device,
+            type(self.group_size), self.group_size, type(self.in_features), self.in_features,
         )
-        _validate_input(x, self.packed_weight, self.in_features)
+
+    def forward(self, x):
+        packed_weight, scales, zeros = self.packed_weight, self.scales, self.zeros
+        # The reference validates the stored state on every call (``linear.py:96-99``), which
+        # costs more host time than a decode kernel runs.  Same checks, same errors, but a state
+        # that has passed is recognised by its key.
+        try:
+            key = self._state_key(packed_weight, scales, zeros)
+        except AttributeError:  # a buffer was replaced by something that is not a tensor
+            key = None
+        if key is None or key != self.__dict__.get("_validated_key"):
+            _validate_packed_weight(packed_weight, scales, zeros, self.group_size, self.in_features)
+            self.__dict__["_validated_key"] = key
+        _validate_input(x, packed_weight, self.in_features)
         if not x.is_contiguous():
             raise ValueError("CUDA input x must be contiguous")
         if not (x.is_cuda and self.group_size == 64):
-            return linear_int4_reference(
-                x, self.packed_weight, self.scales, self.zeros, self.group_size
-            )
+            return linear_int4_reference(x, packed_weight, scales, zeros, self.group_size)
         load_cuda_extension(required=True)
         decode_shape = (
             x.shape[0] == 1 and self.in_features % 64 == 0 and self.out_features % 128 == 0
         )
         if decode_shape:
             return torch.ops.lowbitlinear_ext.w4a16_gemv_warp_vec(
-                x, self.packed_weight, self.scales, self.zeros, self.group_size
+                x, packed_weight, scales, zeros, self.group_size
             )
-        return torch.ops.lowbitlinear_cute_w4a16.gemm(
-            x, self.packed_weight, self.scales, self.zeros
-        )
+        return torch.ops.lowbitlinear_cute_w4a16.gemm(x, packed_weight, scales, zeros)
