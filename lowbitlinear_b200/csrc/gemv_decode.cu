@@ -193,13 +193,14 @@ __global__ void __launch_bounds__(kThreads, 2)
   if (warp == kConsumerWarps) {
     // ------------------------------- producer ------------------------------------------------
     if (lane == 0) {
-      int it = 0;
-      for (int unit = blockIdx.x; unit < p.units; unit += gridDim.x) {
-        const int ks = unit / p.row_tiles;
-        const int n0 = (unit - ks * p.row_tiles) * kRows;
-        for (int st = 0; st < p.stages_per_unit; ++st, ++it) {
-          const int slot = it % p.slots;
-          const int round = it / p.slots;
+      // Slot and round of the ring advance by counting (no division in the loop); the unit's
+      // K segment and row tile likewise.
+      int slot = 0, round = 0;
+      int ks = 0, rt = blockIdx.x;
+      for (int unit = blockIdx.x; unit < p.units; unit += gridDim.x, rt += gridDim.x) {
+        while (rt >= p.row_tiles) rt -= p.row_tiles, ++ks;
+        const int n0 = rt * kRows;
+        for (int st = 0; st < p.stages_per_unit; ++st) {
           if (round > 0) {
             mbar_wait_bounded(&hdr->empty[slot], (round - 1) & 1, abort_flag, p.status,
                               kStatusSkinnyEmptyWait);
@@ -213,6 +214,7 @@ __global__ void __launch_bounds__(kThreads, 2)
           tma_load_3d(base, &tmap_w, 0, stage_index, n0, &hdr->full[slot]);
           tma_load_3d(base + scales_block, &tmap_s, 0, stage_index, n0, &hdr->full[slot]);
           tma_load_3d(base + zeros_block, &tmap_z, 0, stage_index, n0, &hdr->full[slot]);
+          if (++slot == p.slots) slot = 0, ++round;
         }
       }
     }
@@ -250,10 +252,7 @@ __global__ void __launch_bounds__(kThreads, 2)
 
   // Reduction of the CTA's j-th unit by one warp: adds the eight warps' parts (and the two group
   // parities) in a fixed order; lane = activation row * 16 + weight row.
-  auto reduce_unit = [&](int j) {
-    const int unit = blockIdx.x + j * gridDim.x;
-    const int ks = unit / p.row_tiles;
-    const int rt = unit - ks * p.row_tiles;
+  auto reduce_unit = [&](int j, int ks, int rt) {
     const int n0 = rt * kRows;
     const int buffer = j & (kRedBuffers - 1);
     mbar_wait_bounded(&hdr->red_full[buffer], (j / kRedBuffers) & 1, abort_flag, p.status,
@@ -293,13 +292,13 @@ __global__ void __launch_bounds__(kThreads, 2)
     }
   };
 
-  int it = 0;
-  int seq = 0;  // units this CTA has computed
+  int slot = 0, parity = 0;  // ring position, advanced by counting
+  int seq = 0;               // units this CTA has computed
   int current_ks = -1;
-  for (int unit = blockIdx.x; unit < p.units; unit += gridDim.x) {
-    const int ks = unit / p.row_tiles;
-    const int rt = unit - ks * p.row_tiles;
-    const int n0 = rt * kRows;
+  int ks = 0, rt = blockIdx.x;
+  int prev_ks = 0, prev_rt = 0;  // the unit before, reduced one unit late
+  for (int unit = blockIdx.x; unit < p.units; unit += gridDim.x, rt += gridDim.x) {
+    while (rt >= p.row_tiles) rt -= p.row_tiles, ++ks;
 
     if (ks != current_ks) {
       // Activations are the only input the previous kernel may have produced.
@@ -319,10 +318,8 @@ __global__ void __launch_bounds__(kThreads, 2)
 
     float acc_a = 0.0f;  // row n0 + g
     float acc_b = 0.0f;  // row n0 + g + 8
-    for (int st = 0; st < p.stages_per_unit; ++st, ++it) {
-      const int slot = it % p.slots;
-      const int round = it / p.slots;
-      mbar_wait_bounded(&hdr->full[slot], round & 1, abort_flag, p.status, kStatusSkinnyFullWait);
+    for (int st = 0; st < p.stages_per_unit; ++st) {
+      mbar_wait_bounded(&hdr->full[slot], parity, abort_flag, p.status, kStatusSkinnyFullWait);
 
       // 32-bit shared-memory addresses of this lane's operands for macro tile `warp`; macro tile
       // warp + 8 u lies at a fixed distance from it.
@@ -385,6 +382,7 @@ __global__ void __launch_bounds__(kThreads, 2)
       }
       __syncwarp();
       if (lane == 0) mbar_arrive(&hdr->empty[slot]);
+      if (++slot == p.slots) slot = 0, parity ^= 1;
     }
 
     // ---- deposit this warp's part of the unit.  Nobody waits here: the unit is reduced by one
@@ -398,10 +396,11 @@ __global__ void __launch_bounds__(kThreads, 2)
       __syncwarp();
       if (lane == 0) mbar_arrive(&hdr->red_full[seq & (kRedBuffers - 1)]);
     }
-    if (seq > 0 && warp == ((seq - 1) & (kConsumerWarps - 1))) reduce_unit(seq - 1);
+    if (seq > 0 && warp == ((seq - 1) & (kConsumerWarps - 1))) reduce_unit(seq - 1, prev_ks, prev_rt);
+    prev_ks = ks, prev_rt = rt;
     ++seq;
   }
-  if (seq > 0 && warp == ((seq - 1) & (kConsumerWarps - 1))) reduce_unit(seq - 1);
+  if (seq > 0 && warp == ((seq - 1) & (kConsumerWarps - 1))) reduce_unit(seq - 1, prev_ks, prev_rt);
 
   if (p.world == 0) return;
   // ---- fused all-reduce: the last CTA of this GPU tells its peers, waits for theirs, and adds the
