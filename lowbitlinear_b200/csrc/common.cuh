@@ -58,14 +58,38 @@ __device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
 // Waits for the phase with the given parity.  `abort_flag` lives in shared memory: once any
 // thread of the CTA has given up, every later wait returns at once so that the CTA drains and
 // exits instead of hanging.  Returns false if the wait was abandoned.
+// Up to `kSpins` polls of the phase in one tight loop (three instructions per poll).  Each poll may
+// park the warp for up to `kSuspendNs` before it reports "not yet", so a waiting warp leaves the
+// issue slots to the warps that have work.
+template <int kSpins, int kSuspendNs>
+__device__ __forceinline__ bool mbar_poll(uint64_t* bar, uint32_t parity) {
+  uint32_t done;
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t.reg .pred q;\n\t.reg .u32 n;\n\t"
+      "mov.u32 n, 0;\n"
+      "LBL_POLL:\n\t"
+      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3;\n\t"
+      "@p bra LBL_DONE;\n\t"
+      "add.u32 n, n, 1;\n\t"
+      "setp.lt.u32 q, n, %4;\n\t"
+      "@q bra LBL_POLL;\n"
+      "LBL_DONE:\n\t"
+      "selp.u32 %0, 1, 0, p;\n\t}"
+      : "=r"(done)
+      : "r"(smem_addr(bar)), "r"(parity), "r"(static_cast<uint32_t>(kSuspendNs)), "n"(kSpins)
+      : "memory");
+  return done != 0;
+}
+
 __device__ __forceinline__ bool mbar_wait_bounded(uint64_t* bar, uint32_t parity,
                                                   volatile int* abort_flag, int* status_word,
                                                   int status_code) {
   if (mbar_try_wait(bar, parity)) return true;
   const long long start = clock64();
   while (true) {
+    if (mbar_poll<64, 2000>(bar, parity)) return true;
+    // The abort flag and the clock are looked at once per batch of polls.
     if (*abort_flag) return false;
-    if (mbar_try_wait(bar, parity)) return true;
     if (clock64() - start > kWaitLimitCycles) {
       *abort_flag = 1;
       atomicCAS(status_word, 0, status_code);

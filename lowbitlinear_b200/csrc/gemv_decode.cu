@@ -17,6 +17,8 @@
 // Numerics are those of skinny.cu: raw levels q as exact FP16 subnormals, FP32 accumulation,
 //     acc += scale * (sum_k q x - zero * sum_k x)   per group, in FP32.
 #include "common.cuh"
+
+#include <type_traits>
 #include "kernels.h"
 #include "tensor_map.h"
 
@@ -100,6 +102,28 @@ __device__ __forceinline__ uint4 lds128(uint32_t addr) {
                : "r"(addr));
   return v;
 }
+// The same with a compile-time byte offset, which the load instruction carries itself (no address
+// arithmetic per load).
+template <int kOffset>
+__device__ __forceinline__ uint4 lds128_at(uint32_t addr) {
+  uint4 v;
+  asm volatile("ld.shared.v4.u32 {%0, %1, %2, %3}, [%4+%5];"
+               : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w)
+               : "r"(addr), "n"(kOffset));
+  return v;
+}
+template <int kOffset>
+__device__ __forceinline__ float lds_f32_at(uint32_t addr) {
+  float v;
+  asm volatile("ld.shared.f32 %0, [%1+%2];" : "=f"(v) : "r"(addr), "n"(kOffset));
+  return v;
+}
+template <int kOffset>
+__device__ __forceinline__ int lds_s32_at(uint32_t addr) {
+  int v;
+  asm volatile("ld.shared.s32 %0, [%1+%2];" : "=r"(v) : "r"(addr), "n"(kOffset));
+  return v;
+}
 __device__ __forceinline__ float lds_f32(uint32_t addr) {
   float v;
   asm volatile("ld.shared.f32 %0, [%1];" : "=f"(v) : "r"(addr));
@@ -119,7 +143,8 @@ __device__ __forceinline__ uint32_t pack_half2(__half lo, __half hi) {
 // Activation operand of one K segment.  Word w of row m (columns 8w..8w+7) becomes the 16 bytes
 //   (x0, x4) (x1, x5)/16 (x2, x6) (x3, x7)/16
 // in the order the nibble extraction delivers the weights (odd nibbles carry a factor 16), at
-// xf[m * words + w]; sx[group * 2 + m] is the FP32 sum of the group's 64 activations.
+// xf[m * words + w]; sx[group * 2 + m] is the FP32 sum of the group's 64 activations divided by
+// kNibbleUnit.
 __device__ __forceinline__ void build_activation_operand(const DecodeParams& p, int k_begin,
                                                          uint4* xf, float* sx, int tid) {
   const int groups = p.kseg / 64;
@@ -153,7 +178,7 @@ __device__ __forceinline__ void build_activation_operand(const DecodeParams& p, 
     out.z = pack_half2(x2, x6);
     out.w = pack_half2(__hmul(x3, sixteenth), __hmul(x7, sixteenth));
     xf[idx] = out;
-    if ((wd & 7) == 0) sx[(wd >> 3) * 2 + m] = sum;
+    if ((wd & 7) == 0) sx[(wd >> 3) * 2 + m] = sum * (1.0f / kNibbleUnit);  // exact: a power of two
   }
 }
 
@@ -194,7 +219,9 @@ __global__ void __launch_bounds__(kThreads, 2)
     // ------------------------------- producer ------------------------------------------------
     if (lane == 0) {
       // Slot and round of the ring advance by counting (no division in the loop); the unit's
-      // K segment and row tile likewise.
+      // K segment and row tile likewise.  (Prefetching the stages behind the ring into the L2
+      // while the consumers wait for their activations was measured and lost: the prefetches
+      // compete with the loads the consumers are waiting for.)
       int slot = 0, round = 0;
       int ks = 0, rt = blockIdx.x;
       for (int unit = blockIdx.x; unit < p.units; unit += gridDim.x, rt += gridDim.x) {
@@ -332,6 +359,56 @@ __global__ void __launch_bounds__(kThreads, 2)
       const uint32_t xb_addr = xf_addr + static_cast<uint32_t>(st * (p.stage_k / 8) + warp * 16) * 16;
       const uint32_t sx_addr = sx_base + static_cast<uint32_t>(st * (p.stage_k / 64) + 2 * warp) * 8;
 
+      const uint32_t zmeta_a = meta_a + zero_delta;
+      const uint32_t zmeta_b = meta_b + zero_delta;
+      // Arithmetic of one macro tile (16 rows x 128 columns) once its operands are in registers.
+      auto consume = [&](const uint4& wa, const uint4& wb, float scale_a, float scale_b, float zero_a,
+                         float zero_b, float sum_x) {
+        const uint32_t words_a[4] = {wa.x, wa.y, wa.z, wa.w};
+        const uint32_t words_b[4] = {wb.x, wb.y, wb.z, wb.w};
+        // One chain of eight MMAs: the nibble extraction of the next word is independent of it
+        // and the other warps of the scheduler fill the rest of the latency.
+        float d[4];
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+          uint32_t qa[4], qb[4];
+          nibbles_as_subnormal_half2(words_a[i], qa);
+          nibbles_as_subnormal_half2(words_b[i], qb);
+          const uint32_t a0[4] = {qa[0], qb[0], qa[1], qb[1]};
+          const uint32_t a1[4] = {qa[2], qb[2], qa[3], qb[3]};
+          if (i == 0) {
+            mma_m16n8k16(d, a0, xb[i].x, xb[i].y, zero4);
+          } else {
+            mma_m16n8k16(d, a0, xb[i].x, xb[i].y, d);
+          }
+          mma_m16n8k16(d, a1, xb[i].z, xb[i].w, d);
+        }
+        // acc += scale * unit * (sum q x - zero * sum x / unit): the MMA result carries the factor
+        // 1 / kNibbleUnit of the nibble encoding, and sx holds sum x already divided by it.
+        const float qx_a = d[0] + d[1];
+        const float qx_b = d[2] + d[3];
+        acc_a = fmaf(scale_a * kNibbleUnit, fmaf(-zero_a, sum_x, qx_a), acc_a);
+        acc_b = fmaf(scale_b * kNibbleUnit, fmaf(-zero_b, sum_x, qx_b), acc_b);
+      };
+      // Macro tile `warp + 8 u` of the stage; with u known at compile time every load is
+      // base register + immediate.
+      auto macro_tile_at = [&](auto u_const) {
+        constexpr int u = decltype(u_const)::value;
+        const uint4 wa = lds128_at<u * 512>(wa_addr);
+        const uint4 wb = lds128_at<u * 512>(wb_addr);
+        if (feeds_b) {
+          xb[0] = lds128_at<u * 2048>(xb_addr);
+          xb[1] = lds128_at<u * 2048 + 16>(xb_addr);
+          xb[2] = lds128_at<u * 2048 + 32>(xb_addr);
+          xb[3] = lds128_at<u * 2048 + 48>(xb_addr);
+        }
+        const float scale_a = lds_f32_at<u * 64>(meta_a);
+        const float scale_b = lds_f32_at<u * 64>(meta_b);
+        const float zero_a = static_cast<float>(lds_s32_at<u * 64>(zmeta_a));
+        const float zero_b = static_cast<float>(lds_s32_at<u * 64>(zmeta_b));
+        const float sum_x = lds_f32_at<u * 128>(sx_addr);
+        consume(wa, wb, scale_a, scale_b, zero_a, zero_b, sum_x);
+      };
       auto macro_tile = [&](int u) {
         const uint4 wa = lds128(wa_addr + u * 512);
         const uint4 wb = lds128(wb_addr + u * 512);
@@ -341,42 +418,16 @@ __global__ void __launch_bounds__(kThreads, 2)
         }
         const float scale_a = lds_f32(meta_a + u * 64);
         const float scale_b = lds_f32(meta_b + u * 64);
-        const float zero_a = static_cast<float>(lds_s32(meta_a + zero_delta + u * 64));
-        const float zero_b = static_cast<float>(lds_s32(meta_b + zero_delta + u * 64));
+        const float zero_a = static_cast<float>(lds_s32(zmeta_a + u * 64));
+        const float zero_b = static_cast<float>(lds_s32(zmeta_b + u * 64));
         const float sum_x = lds_f32(sx_addr + u * 128);
-
-        const uint32_t words_a[4] = {wa.x, wa.y, wa.z, wa.w};
-        const uint32_t words_b[4] = {wb.x, wb.y, wb.z, wb.w};
-        float d0[4], d1[4];
-#pragma unroll
-        for (int i = 0; i < 4; ++i) {
-          uint32_t qa[4], qb[4];
-          nibbles_as_subnormal_half2(words_a[i], qa);
-          nibbles_as_subnormal_half2(words_b[i], qb);
-          const uint32_t a0[4] = {qa[0], qb[0], qa[1], qb[1]};
-          const uint32_t a1[4] = {qa[2], qb[2], qa[3], qb[3]};
-          if (i == 0) {
-            mma_m16n8k16(d0, a0, xb[i].x, xb[i].y, zero4);
-            mma_m16n8k16(d1, a1, xb[i].z, xb[i].w, zero4);
-          } else {
-            mma_m16n8k16(d0, a0, xb[i].x, xb[i].y, d0);
-            mma_m16n8k16(d1, a1, xb[i].z, xb[i].w, d1);
-          }
-        }
-        // acc += scale * (sum q x) - (scale * zero) * (sum x); the MMA result carries the factor
-        // 1 / kNibbleUnit of the nibble encoding.
-        const float qx_a = (d0[0] + d0[1]) + (d1[0] + d1[1]);
-        const float qx_b = (d0[2] + d0[3]) + (d1[2] + d1[3]);
-        acc_a = fmaf(scale_a * kNibbleUnit, qx_a, acc_a);
-        acc_b = fmaf(scale_b * kNibbleUnit, qx_b, acc_b);
-        acc_a = fmaf(-(scale_a * zero_a), sum_x, acc_a);
-        acc_b = fmaf(-(scale_b * zero_b), sum_x, acc_b);
+        consume(wa, wb, scale_a, scale_b, zero_a, zero_b, sum_x);
       };
       if (macro_per_stage == 16) {  // stage of 2048 columns: two macro tiles per warp
-        macro_tile(0);
-        macro_tile(1);
+        macro_tile_at(std::integral_constant<int, 0>{});
+        macro_tile_at(std::integral_constant<int, 1>{});
       } else if (macro_per_stage == 8) {
-        macro_tile(0);
+        macro_tile_at(std::integral_constant<int, 0>{});
       } else {
         for (int u = 0; warp + 8 * u < macro_per_stage; ++u) macro_tile(u);
       }

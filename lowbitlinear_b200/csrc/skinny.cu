@@ -472,7 +472,7 @@ bool skinny_make_plan(int64_t M, int64_t N, int64_t K, int want_split, int sm_co
   const int fixed = kHeaderBytes + sx_bytes + red_bytes + xf_bytes;
 
   const int ctas_per_sm = std::max(1, std::min(2, env_int("LBL_SKINNY_CTAS_PER_SM", 2)));
-  int budget = ctas_per_sm == 2 ? kSmemBudgetTwoCtas : kSmemBudgetOneCta;
+  int budget = ctas_per_sm == 2 ? env_int("LBL_SKINNY_SMEM_BUDGET", kSmemBudgetTwoCtas) : kSmemBudgetOneCta;
   int per_sm = ctas_per_sm;
   if (fixed + 2 * slot_bytes > budget) {
     budget = kSmemBudgetOneCta;

@@ -33,6 +33,7 @@ __device__ __forceinline__ void tma_load_3d(void* smem_dst, const CUtensorMap* m
       "l"(map), "r"(c0), "r"(c1), "r"(c2), "r"(static_cast<uint32_t>(__cvta_generic_to_shared(bar)))
       : "memory");
 }
+
 #endif
 
 }  // namespace lbl
