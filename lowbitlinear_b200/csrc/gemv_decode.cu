@@ -145,20 +145,32 @@ __device__ __forceinline__ uint32_t pack_half2(__half lo, __half hi) {
 // in the order the nibble extraction delivers the weights (odd nibbles carry a factor 16), at
 // xf[m * words + w]; sx[group * 2 + m] is the FP32 sum of the group's 64 activations divided by
 // kNibbleUnit.
-__device__ __forceinline__ void build_activation_operand(const DecodeParams& p, int k_begin,
-                                                         uint4* xf, float* sx, int tid) {
-  const int groups = p.kseg / 64;
-  const int words_seg = p.kseg / 8;
-  if (p.M < 2) {
+__device__ __forceinline__ void build_activation_operand(const __half* x, int M, int K, int kseg,
+                                                      int k_begin, uint4* xf, float* sx, int tid) {
+  const int groups = kseg / 64;
+  const int words_seg = kseg / 8;
+  if (M < 2) {
     for (int i = tid; i < groups; i += kConsumerThreads) sx[2 * i + 1] = 0.0f;
   }
   const __half sixteenth = __float2half_rn(0.0625f);
-  const int total = p.M * words_seg;  // multiple of 32
+  const int total = M * words_seg;  // multiple of 32, so a warp is never split by `idx < total`
+  // The raw activations go straight to their place in shared memory with asynchronous 16-byte
+  // copies, all issued before any is waited for: the operand costs one trip to the L2 however
+  // long K is (register loads would be kept apart by the shuffles below, one trip per pass).
+  // Each thread then rewrites, in place, the words it copied itself.
   for (int idx = tid; idx < total; idx += kConsumerThreads) {
     const int m = idx / words_seg;
     const int wd = idx - m * words_seg;
-    const uint4 raw =
-        *reinterpret_cast<const uint4*>(p.x + static_cast<size_t>(m) * p.K + k_begin + wd * 8);
+    const __half* src = x + static_cast<size_t>(m) * K + k_begin + wd * 8;
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(smem_addr(&xf[idx])), "l"(src)
+                 : "memory");
+  }
+  asm volatile("cp.async.commit_group;" ::: "memory");
+  asm volatile("cp.async.wait_group 0;" ::: "memory");
+  for (int idx = tid; idx < total; idx += kConsumerThreads) {
+    const int m = idx / words_seg;
+    const int wd = idx - m * words_seg;
+    const uint4 raw = xf[idx];
     const __half2 v01 = *reinterpret_cast<const __half2*>(&raw.x);
     const __half2 v23 = *reinterpret_cast<const __half2*>(&raw.y);
     const __half2 v45 = *reinterpret_cast<const __half2*>(&raw.z);
@@ -338,7 +350,7 @@ __global__ void __launch_bounds__(kThreads, 2)
                          static_cast<size_t>(epoch & 1) * p.capacity_n;
         }
       }
-      build_activation_operand(p, ks * p.kseg, xf, sx, tid);
+      build_activation_operand(p.x, p.M, p.K, p.kseg, ks * p.kseg, xf, sx, tid);
       named_barrier(1, kConsumerThreads);
       current_ks = ks;
     }
