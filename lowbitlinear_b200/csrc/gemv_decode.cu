@@ -234,6 +234,7 @@ __global__ void __launch_bounds__(kThreads, 2)
       // K segment and row tile likewise.  (Prefetching the stages behind the ring into the L2
       // while the consumers wait for their activations was measured and lost: the prefetches
       // compete with the loads the consumers are waiting for.)
+      const uint64_t stream_once = l2_evict_first_policy();
       int slot = 0, round = 0;
       int ks = 0, rt = blockIdx.x;
       for (int unit = blockIdx.x; unit < p.units; unit += gridDim.x, rt += gridDim.x) {
@@ -250,9 +251,9 @@ __global__ void __launch_bounds__(kThreads, 2)
           const int stage_index = ks * p.stages_per_unit + st;
           uint8_t* base = ring + static_cast<size_t>(slot) * p.slot_bytes;
           mbar_arrive_expect_tx(&hdr->full[slot], static_cast<uint32_t>(p.slot_bytes));
-          tma_load_3d(base, &tmap_w, 0, stage_index, n0, &hdr->full[slot]);
-          tma_load_3d(base + scales_block, &tmap_s, 0, stage_index, n0, &hdr->full[slot]);
-          tma_load_3d(base + zeros_block, &tmap_z, 0, stage_index, n0, &hdr->full[slot]);
+          tma_load_3d_hint(base, &tmap_w, 0, stage_index, n0, &hdr->full[slot], stream_once);
+          tma_load_3d_hint(base + scales_block, &tmap_s, 0, stage_index, n0, &hdr->full[slot], stream_once);
+          tma_load_3d_hint(base + zeros_block, &tmap_z, 0, stage_index, n0, &hdr->full[slot], stream_once);
           if (++slot == p.slots) slot = 0, ++round;
         }
       }

@@ -34,6 +34,25 @@ __device__ __forceinline__ void tma_load_3d(void* smem_dst, const CUtensorMap* m
       : "memory");
 }
 
+
+// The same load with an L2 eviction policy (see l2_evict_first_policy): weights are read once
+// per call, so they should be the first lines the L2 gives up, not the activations and results
+// that the neighbouring kernels are about to touch.
+__device__ __forceinline__ void tma_load_3d_hint(void* smem_dst, const CUtensorMap* map, int c0,
+                                                 int c1, int c2, uint64_t* bar, uint64_t policy) {
+  asm volatile(
+      "cp.async.bulk.tensor.3d.shared::cluster.global.tile.mbarrier::complete_tx::bytes.L2::cache_hint "
+      "[%0], [%1, {%2, %3, %4}], [%5], %6;" ::"r"(static_cast<uint32_t>(__cvta_generic_to_shared(smem_dst))),
+      "l"(map), "r"(c0), "r"(c1), "r"(c2), "r"(static_cast<uint32_t>(__cvta_generic_to_shared(bar))),
+      "l"(policy)
+      : "memory");
+}
+
+__device__ __forceinline__ uint64_t l2_evict_first_policy() {
+  uint64_t policy;
+  asm volatile("createpolicy.fractional.L2::evict_first.b64 %0, 1.0;" : "=l"(policy));
+  return policy;
+}
 #endif
 
 }  // namespace lbl
