@@ -28,7 +28,9 @@ namespace {
 constexpr int kRows = 16;
 constexpr int kConsumerWarps = 8;
 constexpr int kConsumerThreads = kConsumerWarps * 32;
-constexpr int kThreads = kConsumerThreads + 32;
+constexpr int kProducerWarp = kConsumerWarps;     // one lane issues the copies
+constexpr int kReducerWarp = kConsumerWarps + 1;  // adds the consumers' parts of each unit, writes y
+constexpr int kThreads = kConsumerThreads + 64;
 constexpr int kMaxSlots = 8;
 constexpr int kHeaderBytes = 384;
 constexpr int kMaxPeers = 8;
@@ -86,7 +88,8 @@ __device__ __forceinline__ float load_relaxed_sys(const float* ptr) {
 struct Header {
   uint64_t full[kMaxSlots];
   uint64_t empty[kMaxSlots];
-  uint64_t red_full[kRedBuffers];  // all eight warps have deposited their part of a unit
+  uint64_t red_full[kRedBuffers];   // all eight warps have deposited their part of a unit
+  uint64_t red_empty[kRedBuffers];  // the reducer has read the buffer
   int abort_flag;
   int ticket;
   int pad[2];
@@ -194,6 +197,24 @@ __device__ __forceinline__ void build_activation_operand(const __half* x, int M,
   }
 }
 
+// The CTA's work list, walked in the same order by the producer, the consumers and the reducer:
+// units a grid apart, unit = K segment `ks` of row tile `rt` (ks-major).  Coordinates advance by
+// counting; there is no division in the loops.
+struct UnitCursor {
+  int unit, next_ks, next_rt;
+  int ks, rt;  // the current unit, valid after next()
+
+  __device__ __forceinline__ UnitCursor() : unit(blockIdx.x), next_ks(0), next_rt(blockIdx.x) {}
+
+  __device__ __forceinline__ bool next(const DecodeParams& p) {
+    if (unit >= p.units) return false;
+    while (next_rt >= p.row_tiles) next_rt -= p.row_tiles, ++next_ks;
+    ks = next_ks, rt = next_rt;
+    unit += gridDim.x, next_rt += gridDim.x;
+    return true;
+  }
+};
+
 __global__ void __launch_bounds__(kThreads, 2)
     w4a16_gemv_decode_kernel(const __grid_constant__ CUtensorMap tmap_w,
                              const __grid_constant__ CUtensorMap tmap_s,
@@ -214,7 +235,10 @@ __global__ void __launch_bounds__(kThreads, 2)
       mbar_init(&hdr->full[s], 1);
       mbar_init(&hdr->empty[s], kConsumerWarps);
     }
-    for (int b = 0; b < kRedBuffers; ++b) mbar_init(&hdr->red_full[b], kConsumerWarps);
+    for (int b = 0; b < kRedBuffers; ++b) {
+      mbar_init(&hdr->red_full[b], kConsumerWarps);
+      mbar_init(&hdr->red_empty[b], 1);
+    }
     hdr->abort_flag = 0;
     hdr->ticket = 0;
     for (int i = 0; i < 4; ++i) hdr->zeros[i] = make_uint4(0u, 0u, 0u, 0u);
@@ -227,7 +251,7 @@ __global__ void __launch_bounds__(kThreads, 2)
   const int scales_block = kRows * p.packed_pitch;
   const int zeros_block = scales_block + kRows * p.meta_pitch;
 
-  if (warp == kConsumerWarps) {
+  if (warp == kProducerWarp) {
     // ------------------------------- producer ------------------------------------------------
     if (lane == 0) {
       // Slot and round of the ring advance by counting (no division in the loop); the unit's
@@ -236,27 +260,96 @@ __global__ void __launch_bounds__(kThreads, 2)
       // compete with the loads the consumers are waiting for.)
       const uint64_t stream_once = l2_evict_first_policy();
       int slot = 0, round = 0;
-      int ks = 0, rt = blockIdx.x;
-      for (int unit = blockIdx.x; unit < p.units; unit += gridDim.x, rt += gridDim.x) {
-        while (rt >= p.row_tiles) rt -= p.row_tiles, ++ks;
-        const int n0 = rt * kRows;
+      auto load_stage = [&](int stage_index, int n0) {
+        if (round > 0) {
+          mbar_wait_bounded(&hdr->empty[slot], (round - 1) & 1, abort_flag, p.status,
+                            kStatusSkinnyEmptyWait);
+        }
+        // The tensor maps view every row as [K / stage_k][stage_k (+ padding)]; padding and
+        // rows past N are zero-filled by the copy engine and cost no traffic.
+        uint8_t* base = ring + static_cast<size_t>(slot) * p.slot_bytes;
+        mbar_arrive_expect_tx(&hdr->full[slot], static_cast<uint32_t>(p.slot_bytes));
+        tma_load_3d_hint(base, &tmap_w, 0, stage_index, n0, &hdr->full[slot], stream_once);
+        tma_load_3d_hint(base + scales_block, &tmap_s, 0, stage_index, n0, &hdr->full[slot], stream_once);
+        tma_load_3d_hint(base + zeros_block, &tmap_z, 0, stage_index, n0, &hdr->full[slot], stream_once);
+        if (++slot == p.slots) slot = 0, ++round;
+      };
+      UnitCursor cur;
+      while (cur.next(p)) {
         for (int st = 0; st < p.stages_per_unit; ++st) {
-          if (round > 0) {
-            mbar_wait_bounded(&hdr->empty[slot], (round - 1) & 1, abort_flag, p.status,
-                              kStatusSkinnyEmptyWait);
-          }
           if (*abort_flag) return;
-          // The tensor maps view every row as [K / stage_k][stage_k (+ padding)]; padding and
-          // rows past N are zero-filled by the copy engine and cost no traffic.
-          const int stage_index = ks * p.stages_per_unit + st;
-          uint8_t* base = ring + static_cast<size_t>(slot) * p.slot_bytes;
-          mbar_arrive_expect_tx(&hdr->full[slot], static_cast<uint32_t>(p.slot_bytes));
-          tma_load_3d_hint(base, &tmap_w, 0, stage_index, n0, &hdr->full[slot], stream_once);
-          tma_load_3d_hint(base + scales_block, &tmap_s, 0, stage_index, n0, &hdr->full[slot], stream_once);
-          tma_load_3d_hint(base + zeros_block, &tmap_z, 0, stage_index, n0, &hdr->full[slot], stream_once);
-          if (++slot == p.slots) slot = 0, ++round;
+          load_stage(cur.ks * p.stages_per_unit + st, cur.rt * kRows);
         }
       }
+    }
+    return;
+  }
+
+  if (warp == kReducerWarp) {
+    // ------------------------------- reducer -------------------------------------------------
+    // Adds the eight consumer warps' parts of each unit in a fixed order (lane = activation row
+    // * 16 + weight row) and writes the result -- or, with split-K, runs the ticket protocol:
+    // partial sums to the scratch, and the CTA that draws a row tile's last ticket adds them in
+    // split order.  The global round trips of that protocol happen here, off the consumers' path.
+    pdl_wait_for_previous_kernel();
+    // With the fused all-reduce this GPU's FP32 result goes to its exchange buffer (the vector
+    // of the next epoch's parity) instead of y.
+    float* exchange_out = nullptr;
+    if (p.world > 0) {
+      const PeerControl* own = reinterpret_cast<const PeerControl*>(p.peers[p.rank]);
+      const unsigned int next_epoch = *reinterpret_cast<const volatile unsigned int*>(&own->epoch) + 1;
+      exchange_out = reinterpret_cast<float*>(p.peers[p.rank] + kPeerDataOffset) +
+                     static_cast<size_t>(next_epoch & 1) * p.capacity_n;
+    }
+    const int row = lane & 15;
+    const int col = lane >> 4;
+    UnitCursor cur;
+    for (int j = 0; cur.next(p); ++j) {
+      const int n0 = cur.rt * kRows;
+      const int buffer = j & (kRedBuffers - 1);
+      mbar_wait_bounded(&hdr->red_full[buffer], (j / kRedBuffers) & 1, abort_flag, p.status,
+                        kStatusSkinnyFullWait);
+      const float* parts = red + buffer * kConsumerWarps * (kRows * 4);
+      float v = 0.0f;
+#pragma unroll
+      for (int w = 0; w < kConsumerWarps; ++w) {
+        v += parts[w * (kRows * 4) + row * 4 + 2 * col] + parts[w * (kRows * 4) + row * 4 + 2 * col + 1];
+      }
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&hdr->red_empty[buffer]);
+      const bool valid = col < p.M && n0 + row < p.N;
+      bool last = true;
+      if (p.nsplit > 1) {
+        if (valid) p.partials[(static_cast<size_t>(cur.ks) * p.M + col) * p.N + n0 + row] = v;
+        __threadfence();
+        __syncwarp();
+        int ticket = 0;
+        if (lane == 0) ticket = atomicAdd(&p.tickets[cur.rt], 1);
+        ticket = __shfl_sync(0xffffffffu, ticket, 0);
+        last = ticket == p.nsplit - 1;
+        if (last) {
+          __threadfence();
+          if (valid) {
+            v = 0.0f;
+            for (int s = 0; s < p.nsplit; ++s) {
+              v += __ldcg(&p.partials[(static_cast<size_t>(s) * p.M + col) * p.N + n0 + row]);
+            }
+          }
+          if (lane == 0) p.tickets[cur.rt] = 0;
+        }
+      }
+      if (last && valid) {
+        if (exchange_out != nullptr) {
+          exchange_out[n0 + row] = v;
+        } else {
+          p.y[static_cast<size_t>(col) * p.N + n0 + row] = __float2half_rn(v);
+        }
+      }
+    }
+    // The all-reduce may only count this CTA as done once its results are out.
+    if (p.world > 0) {
+      __threadfence();
+      named_barrier(2, kConsumerThreads + 32);
     }
     return;
   }
@@ -284,61 +377,16 @@ __global__ void __launch_bounds__(kThreads, 2)
 #pragma unroll
   for (int i = 0; i < 4; ++i) xb[i] = make_uint4(0u, 0u, 0u, 0u);
 
-  // With the fused all-reduce this GPU's FP32 result goes to its exchange buffer (the vector of
-  // the next epoch's parity) instead of y; the last CTA to finish combines the ranks.
+  // Fused all-reduce: the last CTA of this GPU to finish combines the ranks (after the loop).
   PeerControl* ctrl = nullptr;
-  float* exchange_out = nullptr;
   unsigned int epoch = 0;
-
-  // Reduction of the CTA's j-th unit by one warp: adds the eight warps' parts (and the two group
-  // parities) in a fixed order; lane = activation row * 16 + weight row.
-  auto reduce_unit = [&](int j, int ks, int rt) {
-    const int n0 = rt * kRows;
-    const int buffer = j & (kRedBuffers - 1);
-    mbar_wait_bounded(&hdr->red_full[buffer], (j / kRedBuffers) & 1, abort_flag, p.status,
-                      kStatusSkinnyFullWait);
-    const float* parts = red + buffer * kConsumerWarps * (kRows * 4);
-    const int row = lane & 15;
-    const int col = lane >> 4;
-    float v = 0.0f;
-#pragma unroll
-    for (int w = 0; w < kConsumerWarps; ++w) {
-      v += parts[w * (kRows * 4) + row * 4 + 2 * col] + parts[w * (kRows * 4) + row * 4 + 2 * col + 1];
-    }
-    const bool valid = col < p.M && n0 + row < p.N;
-    if (p.nsplit > 1) {
-      if (valid) p.partials[(static_cast<size_t>(ks) * p.M + col) * p.N + n0 + row] = v;
-      __threadfence();
-      __syncwarp();
-      int ticket = 0;
-      if (lane == 0) ticket = atomicAdd(&p.tickets[rt], 1);
-      ticket = __shfl_sync(0xffffffffu, ticket, 0);
-      if (ticket != p.nsplit - 1) return;
-      __threadfence();
-      if (valid) {
-        v = 0.0f;
-        for (int s = 0; s < p.nsplit; ++s) {
-          v += __ldcg(&p.partials[(static_cast<size_t>(s) * p.M + col) * p.N + n0 + row]);
-        }
-      }
-      if (lane == 0) p.tickets[rt] = 0;
-    }
-    if (valid) {
-      if (exchange_out != nullptr) {
-        exchange_out[n0 + row] = v;
-      } else {
-        p.y[static_cast<size_t>(col) * p.N + n0 + row] = __float2half_rn(v);
-      }
-    }
-  };
 
   int slot = 0, parity = 0;  // ring position, advanced by counting
   int seq = 0;               // units this CTA has computed
   int current_ks = -1;
-  int ks = 0, rt = blockIdx.x;
-  int prev_ks = 0, prev_rt = 0;  // the unit before, reduced one unit late
-  for (int unit = blockIdx.x; unit < p.units; unit += gridDim.x, rt += gridDim.x) {
-    while (rt >= p.row_tiles) rt -= p.row_tiles, ++ks;
+  UnitCursor cur;
+  while (cur.next(p)) {
+    const int ks = cur.ks;
 
     if (ks != current_ks) {
       // Activations are the only input the previous kernel may have produced.
@@ -347,8 +395,6 @@ __global__ void __launch_bounds__(kThreads, 2)
         if (p.world > 0) {
           ctrl = reinterpret_cast<PeerControl*>(p.peers[p.rank]);
           epoch = *reinterpret_cast<volatile unsigned int*>(&ctrl->epoch) + 1;
-          exchange_out = reinterpret_cast<float*>(p.peers[p.rank] + kPeerDataOffset) +
-                         static_cast<size_t>(epoch & 1) * p.capacity_n;
         }
       }
       build_activation_operand(p.x, p.M, p.K, p.kseg, ks * p.kseg, xf, sx, tid);
@@ -449,22 +495,23 @@ __global__ void __launch_bounds__(kThreads, 2)
       if (++slot == p.slots) slot = 0, parity ^= 1;
     }
 
-    // ---- deposit this warp's part of the unit.  Nobody waits here: the unit is reduced by one
-    // warp at the end of the *next* unit, when the other warps have long deposited theirs, so the
-    // warps of a CTA never run in lockstep.  kRedBuffers bounds how far they may drift apart; the
-    // ring of stages (at most 6 slots) keeps them closer than that. ---------------------------------
+    // ---- deposit this warp's part of the unit in one of kRedBuffers buffers; the reducer warp
+    // adds the eight parts when all have arrived.  No consumer waits for another here, so the warps
+    // of a CTA never run in lockstep; a buffer is written again only after the reducer has read it.
     {
-      float* mine = red + ((seq & (kRedBuffers - 1)) * kConsumerWarps + warp) * (kRows * 4);
+      const int buffer = seq & (kRedBuffers - 1);
+      if (seq >= kRedBuffers) {
+        mbar_wait_bounded(&hdr->red_empty[buffer], ((seq / kRedBuffers) - 1) & 1, abort_flag, p.status,
+                          kStatusSkinnyEmptyWait);
+      }
+      float* mine = red + (buffer * kConsumerWarps + warp) * (kRows * 4);
       mine[g * 4 + t] = acc_a;
       mine[(g + 8) * 4 + t] = acc_b;
       __syncwarp();
-      if (lane == 0) mbar_arrive(&hdr->red_full[seq & (kRedBuffers - 1)]);
+      if (lane == 0) mbar_arrive(&hdr->red_full[buffer]);
     }
-    if (seq > 0 && warp == ((seq - 1) & (kConsumerWarps - 1))) reduce_unit(seq - 1, prev_ks, prev_rt);
-    prev_ks = ks, prev_rt = rt;
     ++seq;
   }
-  if (seq > 0 && warp == ((seq - 1) & (kConsumerWarps - 1))) reduce_unit(seq - 1, prev_ks, prev_rt);
 
   if (p.world == 0) return;
   // ---- fused all-reduce: the last CTA of this GPU tells its peers, waits for theirs, and adds the
@@ -474,6 +521,8 @@ __global__ void __launch_bounds__(kThreads, 2)
     ctrl = reinterpret_cast<PeerControl*>(p.peers[p.rank]);
     epoch = *reinterpret_cast<volatile unsigned int*>(&ctrl->epoch) + 1;
   }
+  // The reducer warp joins once this CTA's results are in the exchange buffer.
+  named_barrier(2, kConsumerThreads + 32);
   __threadfence();
   named_barrier(1, kConsumerThreads);
   if (tid == 0) hdr->ticket = atomicAdd(&ctrl->done, 1);

@@ -161,6 +161,8 @@ __global__ void __launch_bounds__(kThreads, (NT <= 2 ? 2 : 1))
 
   if (warp == kConsumerWarps) {
     // ------------------------------- producer ------------------------------------------------
+    // Weights are read once per call: first in line for eviction from the L2.
+    const uint64_t stream_once = l2_evict_first_policy();
     int it = 0;
     for (int unit = blockIdx.x; unit < p.units; unit += gridDim.x) {
       const int ks = unit / p.row_tiles;
@@ -182,9 +184,10 @@ __global__ void __launch_bounds__(kThreads, (NT <= 2 ? 2 : 1))
           // as are rows past N.  A box always counts its full size on the barrier.
           uint8_t* base = ring + static_cast<size_t>(slot) * p.slot_bytes;
           mbar_arrive_expect_tx(&hdr->full[slot], static_cast<uint32_t>(p.slot_bytes));
-          tma_load_3d(base, &tmap_w, 0, stage_index, n0, &hdr->full[slot]);
-          tma_load_3d(base + kRows * p.packed_pitch, &tmap_s, 0, stage_index, n0, &hdr->full[slot]);
-          tma_load_3d(base + zeros_block, &tmap_z, 0, stage_index, n0, &hdr->full[slot]);
+          tma_load_3d_hint(base, &tmap_w, 0, stage_index, n0, &hdr->full[slot], stream_once);
+          tma_load_3d_hint(base + kRows * p.packed_pitch, &tmap_s, 0, stage_index, n0, &hdr->full[slot],
+                           stream_once);
+          tma_load_3d_hint(base + zeros_block, &tmap_z, 0, stage_index, n0, &hdr->full[slot], stream_once);
         }
       }
       if (*abort_flag) break;
