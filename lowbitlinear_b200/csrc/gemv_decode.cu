@@ -397,6 +397,9 @@ __global__ void __launch_bounds__(kThreads, 2)
           epoch = *reinterpret_cast<volatile unsigned int*>(&ctrl->epoch) + 1;
         }
       }
+      // A later segment (split-K with several segments per CTA): every warp must be done with
+      // the old operand before it is overwritten.
+      if (current_ks >= 0) named_barrier(1, kConsumerThreads);
       build_activation_operand(p.x, p.M, p.K, p.kseg, ks * p.kseg, xf, sx, tid);
       named_barrier(1, kConsumerThreads);
       current_ks = ks;
