@@ -536,7 +536,7 @@ def run_ours(args):
     # ncu captures of one Gate/Up launch (profiles/), applied to this rank's average launch;
     # traffic follows the weights in proportion, there are no re-reads.
     algorithmic_bytes_per_launch = sum(linear_bytes(m, SHAPES[i][1], SHAPES[i][2]) for i in all_idx) / 4.0 / world
-    traffic_ratio = 1.004 if args.workload == "decode" else 0.767
+    traffic_ratio = 1.006 if args.workload == "decode" else 0.750
     traffic = traffic_ratio * algorithmic_bytes_per_launch
     if args.workload == "decode":
         roofline = {"bound": "hbm", "achieved": value / world, "peak": peaks["hbm_gbs"], "unit": "GB/s",
