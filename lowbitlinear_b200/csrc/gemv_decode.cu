@@ -1,16 +1,18 @@
 // Decode GEMV (M <= 2): the instruction-lean form of the streaming kernel in skinny.cu.
 //
 // Same data movement as skinny.cu -- persistent CTAs, one producer warp, a ring of stages filled
-// by three tiled TMA copies each (packed words, scales, zero points of 16 rows), optional split-K
-// with an ordered reduction -- but the warp MMA is used differently.  With at most two rows of
+// by three tiled TMA copies each (packed words, scales, zero points of 16 rows; evict-first in the
+// L2), optional split-K with an ordered reduction -- plus a reducer warp that adds the eight
+// consumer warps' unit results and writes them out, so the consumers never wait for one another
+// or for global memory.  The warp MMA is used differently.  With at most two rows of
 // activations, six of the eight B columns of an m16n8k16 MMA would be idle.  Here they separate
 // the four lanes of a quad instead: column n of B holds the activations of the k-slots owned by
 // lane n of the quad and zeros elsewhere, so one MMA yields, per weight row, four partial sums
 // that belong to four different 32-column pieces of K.  Each lane can therefore read 16 bytes
 // (32 weights) of its row with a single shared-memory load, and eight MMAs consume 16 rows by
 // 128 columns (two quantisation groups) with
-//     2 loads of weights, 40 integer instructions of nibble extraction, 8 MMAs,
-//     4 predicated loads of activations and about 20 instructions of FP32 scale / zero point,
+//     2 loads of weights, 40 integer instructions of nibble extraction, 8 MMAs in one chain,
+//     4 predicated loads of activations and about 15 instructions of FP32 scale / zero point,
 // roughly a third of the instructions per weight of the general kernel.  Columns 4-7 carry the
 // second activation row when M = 2.
 //
