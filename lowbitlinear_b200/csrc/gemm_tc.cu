@@ -135,34 +135,42 @@ __device__ __forceinline__ void tmem_load_wait() {
 }
 
 // ---- dequantisation of one packed word into eight FP16 weights in column order ----------------
-// (1024 + q) and (1024 + 16 q) are formed with one LOP3 each; subtracting 1024 + zero (or scaling
-// by 1/16 and subtracting 64 + zero) leaves q - zero exactly.  The product with the FP32 scale is
-// rounded to FP32 and then once to FP16, as the reference does.
-__device__ __forceinline__ uint4 dequant_word(uint32_t word, float scale, __half2 bias_lo,
-                                              __half2 bias_hi) {
-  const __half2 sixteenth = __half2half2(__ushort_as_half(0x2C00));  // 1/16
-  const uint32_t hi = word >> 8;
-  uint32_t r0 = (word & 0x000F000Fu) | 0x64006400u;  // 1024 + (q0, q4)
-  uint32_t r1 = (word & 0x00F000F0u) | 0x64006400u;  // 1024 + 16 (q1, q5)
-  uint32_t r2 = (hi & 0x000F000Fu) | 0x64006400u;    // 1024 + (q2, q6)
-  uint32_t r3 = (hi & 0x00F000F0u) | 0x64006400u;    // 1024 + 16 (q3, q7)
-  const __half2 d04 = __hsub2(*reinterpret_cast<__half2*>(&r0), bias_lo);
-  const __half2 d15 = __hfma2(*reinterpret_cast<__half2*>(&r1), sixteenth, bias_hi);
-  const __half2 d26 = __hsub2(*reinterpret_cast<__half2*>(&r2), bias_lo);
-  const __half2 d37 = __hfma2(*reinterpret_cast<__half2*>(&r3), sixteenth, bias_hi);
-  const float2 f04 = __half22float2(d04);
-  const float2 f15 = __half22float2(d15);
-  const float2 f26 = __half22float2(d26);
-  const float2 f37 = __half22float2(d37);
-  const __half2 w01 = __floats2half2_rn(__fmul_rn(f04.x, scale), __fmul_rn(f15.x, scale));
-  const __half2 w23 = __floats2half2_rn(__fmul_rn(f26.x, scale), __fmul_rn(f37.x, scale));
-  const __half2 w45 = __floats2half2_rn(__fmul_rn(f04.y, scale), __fmul_rn(f15.y, scale));
-  const __half2 w67 = __floats2half2_rn(__fmul_rn(f26.y, scale), __fmul_rn(f37.y, scale));
+// A nibble masked in place and OR-ed into the mantissa of 2^23 is the float 2^23 + 16^i q (i = its
+// position in the 16-bit half of the word), with one LOP3 and no shift; subtracting 2^23 + 16^i z
+// leaves 16^i (q - z) exactly, and the product with 16^-i scale has exactly the bits of
+// float(q - z) * scale, since both factors only moved by a power of two.  It is rounded to FP32 and
+// then once to FP16, as the reference does.  Additions and multiplications are packed pairs.
+struct GroupConstants {
+  float2 neg_c01, neg_c23;  // -(2^23 + 16^i zero), i = 0..3
+  float2 s01, s23;          // 16^-i scale
+};
+
+__device__ __forceinline__ GroupConstants group_constants(float scale, int zero) {
+  const float z = static_cast<float>(zero);
+  GroupConstants g;
+  g.neg_c01 = make_float2(-(8388608.0f + z), -(8388608.0f + 16.0f * z));
+  g.neg_c23 = make_float2(-(8388608.0f + 256.0f * z), -(8388608.0f + 4096.0f * z));
+  g.s01 = make_float2(scale, scale * 0.0625f);
+  g.s23 = make_float2(scale * 0.00390625f, scale * 0.000244140625f);
+  return g;
+}
+
+__device__ __forceinline__ uint32_t two_weights(uint32_t bits, uint32_t mask_a, uint32_t mask_b,
+                                                float2 neg_c, float2 s) {
+  const float2 f = make_float2(__uint_as_float((bits & mask_a) | 0x4B000000u),
+                               __uint_as_float((bits & mask_b) | 0x4B000000u));
+  const float2 w = __fmul2_rn(__fadd2_rn(f, neg_c), s);
+  const __half2 h = __floats2half2_rn(w.x, w.y);
+  return *reinterpret_cast<const uint32_t*>(&h);
+}
+
+__device__ __forceinline__ uint4 dequant_word(uint32_t word, const GroupConstants& g) {
+  const uint32_t hi = word >> 16;
   uint4 out;
-  out.x = *reinterpret_cast<const uint32_t*>(&w01);
-  out.y = *reinterpret_cast<const uint32_t*>(&w23);
-  out.z = *reinterpret_cast<const uint32_t*>(&w45);
-  out.w = *reinterpret_cast<const uint32_t*>(&w67);
+  out.x = two_weights(word, 0x000Fu, 0x00F0u, g.neg_c01, g.s01);
+  out.y = two_weights(word, 0x0F00u, 0xF000u, g.neg_c23, g.s23);
+  out.z = two_weights(hi, 0x000Fu, 0x00F0u, g.neg_c01, g.s01);
+  out.w = two_weights(hi, 0x0F00u, 0xF000u, g.neg_c23, g.s23);
   return out;
 }
 
@@ -286,17 +294,14 @@ __global__ void __launch_bounds__(kThreads, 1)
           mbar_wait_bounded(&bars->empty[s], (round - 1) & 1, abort_flag, p.status,
                             kStatusGemmWait + 4);
         }
-        const __half z_lo = __int2half_rn(1024 + zp[j]);    // exact: integers up to 2048
-        const __half z_hi = __int2half_rn(-(64 + zp[j]));
-        const __half2 bias_lo = __half2half2(z_lo);
-        const __half2 bias_hi = __half2half2(z_hi);
+        const GroupConstants group = group_constants(sc[j], zp[j]);
         uint8_t* dst = smem_b + s * kStageBytesB + row_offset;
         const uint4 wa = cur.words[2 * j];
         const uint4 wb = cur.words[2 * j + 1];
         const uint32_t w[8] = {wa.x, wa.y, wa.z, wa.w, wb.x, wb.y, wb.z, wb.w};
 #pragma unroll
         for (int c = 0; c < 8; ++c) {
-          const uint4 out = dequant_word(w[c], sc[j], bias_lo, bias_hi);
+          const uint4 out = dequant_word(w[c], group);
           *reinterpret_cast<uint4*>(dst + ((static_cast<uint32_t>(c) ^ swz) << 4)) = out;
         }
         fence_async_proxy();  // generic-proxy writes -> visible to the tensor core's reads

@@ -94,36 +94,53 @@ __device__ __forceinline__ void build_activation_operand(const KernelParams& p, 
   }
   const __half sixteenth = __float2half_rn(0.0625f);
   const int total = p.M * words_seg;  // multiple of 32: whole warps stay together below
-  for (int idx = tid; idx < total; idx += kConsumerThreads) {
-    const int m = idx / words_seg;
-    const int wd = idx - m * words_seg;
-    const uint4 raw =
-        *reinterpret_cast<const uint4*>(p.x + static_cast<size_t>(m) * p.K + k_begin + wd * 8);
-    const __half2 v01 = *reinterpret_cast<const __half2*>(&raw.x);
-    const __half2 v23 = *reinterpret_cast<const __half2*>(&raw.y);
-    const __half2 v45 = *reinterpret_cast<const __half2*>(&raw.z);
-    const __half2 v67 = *reinterpret_cast<const __half2*>(&raw.w);
-    const __half x0 = __low2half(v01), x1 = __high2half(v01);
-    const __half x2 = __low2half(v23), x3 = __high2half(v23);
-    const __half x4 = __low2half(v45), x5 = __high2half(v45);
-    const __half x6 = __low2half(v67), x7 = __high2half(v67);
-    float sum = ((__half2float(x0) + __half2float(x1)) + (__half2float(x2) + __half2float(x3))) +
-                ((__half2float(x4) + __half2float(x5)) + (__half2float(x6) + __half2float(x7)));
-    sum += __shfl_xor_sync(0xffffffffu, sum, 1);
-    sum += __shfl_xor_sync(0xffffffffu, sum, 2);
-    sum += __shfl_xor_sync(0xffffffffu, sum, 4);
-    const int group = wd >> 3;
-    const int wq = wd & 7;
-    const int t = wq >> 1;
-    const int h = wq & 1;
-    uint2 step0, step1;
-    step0.x = pack_half2(x0, x4);
-    step0.y = pack_half2(__hmul(x1, sixteenth), __hmul(x5, sixteenth));
-    step1.x = pack_half2(x2, x6);
-    step1.y = pack_half2(__hmul(x3, sixteenth), __hmul(x7, sixteenth));
-    xf[((group * 4 + 2 * h) * p.M + m) * 4 + t] = step0;
-    xf[((group * 4 + 2 * h + 1) * p.M + m) * 4 + t] = step1;
-    if (wq == 0) sx[group * MC + m] = sum;
+  // The loads of a batch are issued before the first one is used: one trip to the L2 per batch
+  // instead of one per pass (the shuffles would otherwise keep each pass's load behind the
+  // arithmetic of the pass before).
+  constexpr int kBatch = 4;
+  for (int first = 0; first < total; first += kBatch * kConsumerThreads) {
+    uint4 raw[kBatch];
+#pragma unroll
+    for (int j = 0; j < kBatch; ++j) {
+      const int idx = first + j * kConsumerThreads + tid;
+      if (idx < total) {
+        const int m = idx / words_seg;
+        const int wd = idx - m * words_seg;
+        raw[j] = __ldcg(reinterpret_cast<const uint4*>(p.x + static_cast<size_t>(m) * p.K + k_begin + wd * 8));
+      }
+    }
+#pragma unroll
+    for (int j = 0; j < kBatch; ++j) {
+      const int idx = first + j * kConsumerThreads + tid;
+      if (idx >= total) break;
+      const int m = idx / words_seg;
+      const int wd = idx - m * words_seg;
+      const __half2 v01 = *reinterpret_cast<const __half2*>(&raw[j].x);
+      const __half2 v23 = *reinterpret_cast<const __half2*>(&raw[j].y);
+      const __half2 v45 = *reinterpret_cast<const __half2*>(&raw[j].z);
+      const __half2 v67 = *reinterpret_cast<const __half2*>(&raw[j].w);
+      const __half x0 = __low2half(v01), x1 = __high2half(v01);
+      const __half x2 = __low2half(v23), x3 = __high2half(v23);
+      const __half x4 = __low2half(v45), x5 = __high2half(v45);
+      const __half x6 = __low2half(v67), x7 = __high2half(v67);
+      float sum = ((__half2float(x0) + __half2float(x1)) + (__half2float(x2) + __half2float(x3))) +
+                  ((__half2float(x4) + __half2float(x5)) + (__half2float(x6) + __half2float(x7)));
+      sum += __shfl_xor_sync(0xffffffffu, sum, 1);
+      sum += __shfl_xor_sync(0xffffffffu, sum, 2);
+      sum += __shfl_xor_sync(0xffffffffu, sum, 4);
+      const int group = wd >> 3;
+      const int wq = wd & 7;
+      const int t = wq >> 1;
+      const int h = wq & 1;
+      uint2 step0, step1;
+      step0.x = pack_half2(x0, x4);
+      step0.y = pack_half2(__hmul(x1, sixteenth), __hmul(x5, sixteenth));
+      step1.x = pack_half2(x2, x6);
+      step1.y = pack_half2(__hmul(x3, sixteenth), __hmul(x7, sixteenth));
+      xf[((group * 4 + 2 * h) * p.M + m) * 4 + t] = step0;
+      xf[((group * 4 + 2 * h + 1) * p.M + m) * 4 + t] = step1;
+      if (wq == 0) sx[group * MC + m] = sum;
+    }
   }
 }
 
@@ -163,14 +180,12 @@ __global__ void __launch_bounds__(kThreads, (NT <= 2 ? 2 : 1))
     // ------------------------------- producer ------------------------------------------------
     // Weights are read once per call: first in line for eviction from the L2.
     const uint64_t stream_once = l2_evict_first_policy();
-    int it = 0;
+    int slot = 0, round = 0;  // ring position, advanced by counting
     for (int unit = blockIdx.x; unit < p.units; unit += gridDim.x) {
       const int ks = unit / p.row_tiles;
       const int rt = unit - ks * p.row_tiles;
       const int n0 = rt * kRows;
-      for (int st = 0; st < p.stages_per_unit; ++st, ++it) {
-        const int slot = it % p.slots;
-        const int round = it / p.slots;
+      for (int st = 0; st < p.stages_per_unit; ++st) {
         if (round > 0) {
           mbar_wait_bounded(&hdr->empty[slot], (round - 1) & 1, abort_flag, p.status,
                             kStatusSkinnyEmptyWait);
@@ -189,6 +204,7 @@ __global__ void __launch_bounds__(kThreads, (NT <= 2 ? 2 : 1))
                            stream_once);
           tma_load_3d_hint(base + zeros_block, &tmap_z, 0, stage_index, n0, &hdr->full[slot], stream_once);
         }
+        if (++slot == p.slots) slot = 0, ++round;
       }
       if (*abort_flag) break;
     }
@@ -202,7 +218,7 @@ __global__ void __launch_bounds__(kThreads, (NT <= 2 ? 2 : 1))
   const int groups_per_stage = p.stage_k / 64;
   const float zero4[4] = {0.0f, 0.0f, 0.0f, 0.0f};
 
-  int it = 0;
+  int slot = 0, parity = 0;  // ring position, advanced by counting
   int current_ks = -1;
   for (int unit = blockIdx.x; unit < p.units; unit += gridDim.x) {
     const int ks = unit / p.row_tiles;
@@ -224,10 +240,8 @@ __global__ void __launch_bounds__(kThreads, (NT <= 2 ? 2 : 1))
       for (int i = 0; i < 4; ++i) acc[nt][i] = 0.0f;
     }
 
-    for (int st = 0; st < p.stages_per_unit; ++st, ++it) {
-      const int slot = it % p.slots;
-      const int round = it / p.slots;
-      mbar_wait_bounded(&hdr->full[slot], round & 1, abort_flag, p.status, kStatusSkinnyFullWait);
+    for (int st = 0; st < p.stages_per_unit; ++st) {
+      mbar_wait_bounded(&hdr->full[slot], parity, abort_flag, p.status, kStatusSkinnyFullWait);
 
       const uint8_t* base = ring + static_cast<size_t>(slot) * p.slot_bytes;
       const uint8_t* row_a = base + g * p.packed_pitch + t * 8;
@@ -325,6 +339,7 @@ __global__ void __launch_bounds__(kThreads, (NT <= 2 ? 2 : 1))
       }
       __syncwarp();
       if (lane == 0) mbar_arrive(&hdr->empty[slot]);
+      if (++slot == p.slots) slot = 0, parity ^= 1;
     }
 
     // ---- cross-warp reduction of the unit, fixed order ---------------------------------------
