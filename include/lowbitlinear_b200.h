@@ -43,6 +43,8 @@ extern "C" {
 #define LBL_PATH_GEMV 2         /* streaming skinny kernel, M <= 32, one pass over K        */
 #define LBL_PATH_GEMV_SPLITK 3  /* same kernel, K split across CTAs, ordered reduction      */
 #define LBL_PATH_GEMM_TC 4      /* TMA + tcgen05 tensor-core GEMM, FP32 accumulators in TMEM */
+#define LBL_PATH_GEMM_TC_SMALL 5 /* tcgen05 GEMM for M <= 128: weights on the M side of the MMA,
+                                    K cut into slices (uses the scratch when there is one)   */
 
 /* Flags. */
 #define LBL_FLAG_PDL 1u            /* programmatic dependent launch: weights are prefetched

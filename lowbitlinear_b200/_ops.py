@@ -14,13 +14,14 @@ import threading
 
 import torch
 
-PATH_AUTO, PATH_GENERIC, PATH_GEMV, PATH_GEMV_SPLITK, PATH_GEMM_TC = range(5)
+PATH_AUTO, PATH_GENERIC, PATH_GEMV, PATH_GEMV_SPLITK, PATH_GEMM_TC, PATH_GEMM_TC_SMALL = range(6)
 PATH_NAMES = {
     PATH_AUTO: "auto",
     PATH_GENERIC: "generic",
     PATH_GEMV: "gemv",
     PATH_GEMV_SPLITK: "gemv_splitk",
     PATH_GEMM_TC: "gemm_tc",
+    PATH_GEMM_TC_SMALL: "gemm_tc_small",
 }
 FLAG_PDL = 1
 FLAG_ROUND_WEIGHTS = 2
@@ -131,7 +132,9 @@ def _workspace(device, stream, m, n, k, path=PATH_AUTO, exact=False):
 def _run(device, stream, m, n, k, path, call):
     """``call(ws, ws_bytes) -> rc`` with the cached scratch; if the library finds it too small,
     once more with a buffer of the size it asks for (nothing was launched by the first try)."""
-    rc = call(*_workspace(device, stream, m, n, k, path))
+    # The tensor-core kernels use scratch when it is there and do without otherwise, so problems
+    # that may go to them (more than 8 rows of activations) ask for their exact need.
+    rc = call(*_workspace(device, stream, m, n, k, path, exact=m > 8))
     if rc == ERR_WORKSPACE:
         rc = call(*_workspace(device, stream, m, n, k, path, exact=True))
     _check(rc)

@@ -100,6 +100,14 @@ int tc_min_m() {
   return std::atoi(v);
 }
 
+// From this M on, shapes the small-M tensor-core GEMM can serve go to it instead of the streaming
+// kernel (which it overtakes as the rows of activations fill more MMA columns).
+int tc_small_min_m() {
+  const char* v = std::getenv("LBL_TC_SMALL_MIN_M");
+  if (v == nullptr || *v == '\0') return 9;
+  return std::atoi(v);
+}
+
 int select_path(int64_t M, int64_t N, int64_t K, int op, int sm_count) {
   (void)op;
   if (M <= 0 || N <= 0 || K <= 0) return LBL_PATH_GENERIC;
@@ -107,7 +115,12 @@ int select_path(int64_t M, int64_t N, int64_t K, int op, int sm_count) {
   const bool tc_ok = lbl::gemm_tc_supports(M, N, K);
   // Measured crossover (B200): the streaming kernels win up to M = 16; from M = 9 the
   // tensor-core GEMM already wins when N is large enough to fill the SMs with 256-wide tiles.
+  // Measured (B200): with 9..128 rows of activations the small-M tensor-core GEMM wins wherever
+  // the 256-wide tiles of the large one cannot fill the SMs (N < 16384), and up to M = 32 beyond.
   const bool wide = N >= 16384;
+  if (M >= tc_small_min_m() && lbl::gemm_tc_small_supports(M, N, K) && (!wide || M <= 32 || !tc_ok)) {
+    return LBL_PATH_GEMM_TC_SMALL;
+  }
   if (tc_ok && (M >= tc_min_m() || (wide && M >= 9) || !skinny_ok)) return LBL_PATH_GEMM_TC;
   if (skinny_ok) {
     lbl::SkinnyPlan plan;
@@ -202,6 +215,14 @@ int run_linear(const void* X, const int32_t* packed_w, const float* scales, cons
       err = lbl::launch_gemm_tc(prob, info.status_word, cu_stream);
       break;
     }
+    case LBL_PATH_GEMM_TC_SMALL: {
+      if (!lbl::gemm_tc_small_supports(M, N, K)) {
+        return fail(LBL_ERR_UNSUPPORTED, "small-M tensor-core GEMM cannot serve M=%lld N=%lld K=%lld (needs M <= 128, N %% 128 == 0, K %% 256 == 0)", (long long)M, (long long)N, (long long)K);
+      }
+      err = lbl::launch_gemm_tc_small(prob, info.status_word, cu_stream, workspace, workspace_bytes,
+                                      info.sm_count);
+      break;
+    }
     default:
       return fail(LBL_ERR_INVALID, "unknown path %d", path);
   }
@@ -242,6 +263,7 @@ size_t lbl_w4a16_workspace_bytes(int64_t M, int64_t N, int64_t K, int path) {
     path = forced_path_from_env();
     if (path == LBL_PATH_AUTO) path = select_path(M, N, K, 0, sms);
   }
+  if (path == LBL_PATH_GEMM_TC_SMALL) return lbl::gemm_tc_small_workspace_bytes(M, N, K, sms);
   if (path != LBL_PATH_GEMV && path != LBL_PATH_GEMV_SPLITK) return 0;
   lbl::SkinnyPlan plan;
   const int want = path == LBL_PATH_GEMV_SPLITK ? 2 : -1;

@@ -82,4 +82,12 @@ cudaError_t launch_skinny(const Problem& p, const SkinnyPlan& plan, float* parti
 bool gemm_tc_supports(int64_t M, int64_t N, int64_t K);
 cudaError_t launch_gemm_tc(const Problem& p, int* status_word, cudaStream_t stream);
 
+// ----- tcgen05 GEMM for M <= 128, weights on the M side of the MMA (gemm_tc_small.cu) ----------
+bool gemm_tc_small_supports(int64_t M, int64_t N, int64_t K);
+// Scratch that lets K be cut into slices (0: the shape needs none).  Layout: the fixed region of
+// arrival counters, then FP32 partial tiles.  Optional: without it one CTA walks the whole of K.
+size_t gemm_tc_small_workspace_bytes(int64_t M, int64_t N, int64_t K, int sm_count);
+cudaError_t launch_gemm_tc_small(const Problem& p, int* status_word, cudaStream_t stream, void* workspace,
+                                 size_t workspace_bytes, int sm_count);
+
 }  // namespace lbl

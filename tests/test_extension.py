@@ -81,7 +81,10 @@ def test_dispatcher_choices_and_scratch_sizes():
         assert name(8, 4096, 12288) == "gemv_splitk"   # activations of one segment must fit on chip
         # Prefill shapes go to the tensor cores; ragged shapes to the masked kernel.
         assert name(2048, 24576, 4096) == "gemm_tc"
-        assert name(128, 4096, 12288) == "gemm_tc"
+        assert name(128, 4096, 12288) == "gemm_tc_small"   # weights on the M side of the MMA
+        assert name(16, 24576, 4096) == "gemm_tc_small"
+        assert name(64, 24576, 4096) == "gemm_tc"          # wide N: 256-wide tiles fill the SMs
+        assert name(129, 4096, 12288) == "gemm_tc"
         assert name(5, 9, 70) == "generic"
         assert name(1, 129, 64) == "generic"
         assert name(2048, 129, 4096) == "generic"

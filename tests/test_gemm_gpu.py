@@ -108,15 +108,56 @@ def test_tensor_core_path_against_oracle(m, n, k, cuda_ops):
     torch.testing.assert_close(y.cpu(), oracle_linear(x, packed, scales, zeros, mma=True), atol=ATOL, rtol=RTOL)
 
 
+@pytest.mark.parametrize("m,n,k", [(1, 128, 256), (9, 128, 512), (16, 256, 1024), (17, 384, 2048), (33, 4096, 4096),
+                                   (64, 1024, 12288), (100, 640, 768), (128, 2048, 4096)])
+def test_small_m_tensor_core_path_against_oracle(m, n, k, cuda_ops, monkeypatch):
+    """tcgen05 GEMM with the weights on the M side of the MMA (M <= 128): FP16-rounded weights as
+    in the reference GEMM; K cut into slices that meet in the scratch, bit-reproducible; without
+    scratch one CTA per row block gives the same answer within the tolerance."""
+    import ctypes
+
+    from lowbitlinear_b200 import _ops
+    from lowbitlinear_b200._extension import native
+
+    x, packed, scales, zeros = seeded_layer(m, n, k, seed=m + n + k, std=1.0, device=cuda_ops)
+    expected = oracle_linear(x, packed, scales, zeros, mma=True)
+    # Unit-variance weights: outputs of magnitude sqrt(K), where one FP16 step is 2e-3 .. 8e-3 and
+    # the order of the FP32 additions decides the last bit; the absolute tolerance follows.
+    atol = ATOL * (4 if k > 4096 else 1)
+    runs = [_ops.linear_forced(x, packed, scales, zeros, _ops.PATH_GEMM_TC_SMALL) for _ in range(3)]
+    assert all(taken == _ops.PATH_GEMM_TC_SMALL for _, taken in runs)
+    assert torch.equal(runs[0][0], runs[1][0]) and torch.equal(runs[0][0], runs[2][0])
+    torch.testing.assert_close(runs[0][0].cpu(), expected, atol=atol, rtol=RTOL)
+    y = torch.empty(m, n, dtype=torch.float16, device=cuda_ops)
+    rc = native().lbl_w4a16_linear(x.data_ptr(), packed.data_ptr(), scales.data_ptr(), zeros.data_ptr(),
+                                   y.data_ptr(), m, n, k, 1, _ops.PATH_GEMM_TC_SMALL, None, 0, 0,
+                                   cuda_ops.index, torch.cuda.current_stream().cuda_stream, None)
+    assert rc == 0
+    torch.testing.assert_close(y.cpu(), expected, atol=atol, rtol=RTOL)
+    monkeypatch.setenv("LBL_GEMM_SMALL_SLICES", "1")
+    unsliced, _ = _ops.linear_forced(x, packed, scales, zeros, _ops.PATH_GEMM_TC_SMALL)
+    assert torch.equal(unsliced, y)
+
+
+def test_small_m_tensor_core_path_rejects_other_shapes(cuda_ops):
+    from lowbitlinear_b200 import _ops
+
+    for m, n, k in ((129, 256, 256), (8, 192, 256), (8, 256, 320)):
+        x, packed, scales, zeros = seeded_layer(m, n, k, seed=1, device=cuda_ops)
+        with pytest.raises(RuntimeError, match="small-M tensor-core GEMM cannot serve"):
+            _ops.linear_forced(x, packed, scales, zeros, _ops.PATH_GEMM_TC_SMALL)
+
+
 @pytest.mark.parametrize("name,n,k,seed", [("gate_up", 24576, 4096, 2), ("down", 4096, 12288, 3)])
-@pytest.mark.parametrize("m", [128, 2048])
+@pytest.mark.parametrize("m", [16, 64, 128, 2048])
 def test_prefill_shapes_meet_the_benchmark_tolerance(name, n, k, seed, m, cuda_ops):
     """Benchmark config 4 at full size, checked against an FP32 evaluation on the GPU
     (TF32 off) and, on a slice of rows, against the numpy oracle."""
     from lowbitlinear_b200 import QuantizedLinear, _ops
 
     x, packed, scales, zeros = seeded_layer(m, n, k, seed=seed, device=cuda_ops)
-    assert _ops.select_path(m, n, k) == _ops.PATH_GEMM_TC
+    small = m <= 32 or (m <= 128 and n < 16384)
+    assert _ops.select_path(m, n, k) == (_ops.PATH_GEMM_TC_SMALL if small else _ops.PATH_GEMM_TC)
     layer = QuantizedLinear(packed, scales, zeros, in_features=k)
     y = layer(x)
     assert_north_star_parity(y, torch_fp32_linear(x, packed, scales, zeros))
