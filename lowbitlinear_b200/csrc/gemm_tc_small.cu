@@ -17,11 +17,11 @@
 //
 //   warp 0      one thread issues the 2-D TMA load of the X block (BT rows x 64 columns, 128-byte
 //               swizzle, rows past M zero-filled) per stage.
-//   warps 2-5   thread r owns weight row n0 + r: registers <- packed words and metadata of 256
-//               columns at a time, one group dequantised per stage into a 128-byte row of the
+//   warps 2-9   two threads per weight row: registers <- packed words and metadata of 256 columns
+//               at a time, half a group each dequantised per stage into the row's 128 bytes of the
 //               K-major, swizzled A tile (exact policy, tc_common.cuh).
 //   warp 1      one thread issues 4 tcgen05.mma (M = 128, N = BT, K = 16) per stage.
-//   warps 2-5   epilogue: tcgen05.ld of the accumulator, lane = weight row, so that for each token
+//   warps 2-9   epilogue: tcgen05.ld of the accumulator, lane = weight row, so that for each token
 //               a warp stores 32 neighbouring outputs.
 //
 // Every wait on an mbarrier is bounded.  Shapes: N % 128 == 0, K % 256 == 0, 1 <= M <= 128.
@@ -41,7 +41,7 @@ constexpr int kStages = 3;
 constexpr int kMaxTokens = 128;
 constexpr int kStageBytesW = kRowsW * kBK * 2;      // 16 KB
 constexpr int kStageBytesX = kMaxTokens * kBK * 2;  // 16 KB (BT * 128 bytes are used)
-constexpr int kDequantWarps = 4;
+constexpr int kDequantWarps = 8;  // two threads per weight row, half a group each
 constexpr int kThreads = 32 * (2 + kDequantWarps);
 constexpr int kTmemCols = 128;
 constexpr int kBarrierBytes = 256;
@@ -153,20 +153,36 @@ __global__ void __launch_bounds__(kThreads, 2)
     }
   } else {
     // ------------------------------- dequantisation warps --------------------------------------
-    const int row = (warp - 2) * 32 + lane;  // row of the weight tile, 0..127
+    const int worker = (warp - 2) * 32 + lane;  // 0..255
+    const int row = worker >> 1;                // row of the weight tile, 0..127
+    const int half = worker & 1;                // which 32 columns of each group this thread owns
     const size_t n = static_cast<size_t>(n0 + row);
-    const uint32_t* packed_row = p.packed + n * (p.K / 8);
+    const uint32_t* packed_row = p.packed + n * (p.K / 8) + half * 4;
     const float* scale_row = p.scales + n * (p.K / 64);
     const int32_t* zero_row = p.zeros + n * (p.K / 64);
     const uint32_t row_offset = (row >> 3) * 1024 + (row & 7) * 128;
     const uint32_t swz = row & 7;
 
-    RowPrefetch buf[2];
-    prefetch_row(buf[0], packed_row, scale_row, zero_row, sb_begin);
+    // Registers <- this thread's packed words and the row's metadata of one super block (256
+    // columns: four groups, four words of each).
+    struct HalfRowPrefetch {
+      uint4 words[4];
+      float4 scale;
+      int4 zero;
+    };
+    auto prefetch = [&](HalfRowPrefetch& buf, int super_block) {
+      const uint32_t* src = packed_row + super_block * 32;
+#pragma unroll
+      for (int j = 0; j < 4; ++j) buf.words[j] = __ldg(reinterpret_cast<const uint4*>(src + j * 8));
+      buf.scale = __ldg(reinterpret_cast<const float4*>(scale_row + super_block * 4));
+      buf.zero = __ldg(reinterpret_cast<const int4*>(zero_row + super_block * 4));
+    };
+    HalfRowPrefetch buf[2];
+    prefetch(buf[0], sb_begin);
 
     // `sb` counts this CTA's super blocks from 0; the data come from super block sb_begin + sb.
     const int super_blocks = sb_end - sb_begin;
-    auto run_super_block = [&](const RowPrefetch& cur, int sb) {
+    auto run_super_block = [&](const HalfRowPrefetch& cur, int sb) {
       const float sc[4] = {cur.scale.x, cur.scale.y, cur.scale.z, cur.scale.w};
       const int zp[4] = {cur.zero.x, cur.zero.y, cur.zero.z, cur.zero.w};
 #pragma unroll
@@ -179,13 +195,11 @@ __global__ void __launch_bounds__(kThreads, 2)
         }
         const GroupConstants group = group_constants(sc[j], zp[j]);
         uint8_t* dst = smem_w + s * kStageBytesW + row_offset;
-        const uint4 wa = cur.words[2 * j];
-        const uint4 wb = cur.words[2 * j + 1];
-        const uint32_t w[8] = {wa.x, wa.y, wa.z, wa.w, wb.x, wb.y, wb.z, wb.w};
+        const uint32_t w[4] = {cur.words[j].x, cur.words[j].y, cur.words[j].z, cur.words[j].w};
 #pragma unroll
-        for (int c = 0; c < 8; ++c) {
+        for (int c = 0; c < 4; ++c) {
           const uint4 out = dequant_word(w[c], group);
-          *reinterpret_cast<uint4*>(dst + ((static_cast<uint32_t>(c) ^ swz) << 4)) = out;
+          *reinterpret_cast<uint4*>(dst + ((static_cast<uint32_t>(half * 4 + c) ^ swz) << 4)) = out;
         }
         fence_async_proxy();  // generic-proxy writes -> visible to the tensor core's reads
         __syncwarp();
@@ -194,10 +208,10 @@ __global__ void __launch_bounds__(kThreads, 2)
     };
 
     for (int sb = 0; sb < super_blocks; sb += 2) {
-      if (sb + 1 < super_blocks) prefetch_row(buf[1], packed_row, scale_row, zero_row, sb_begin + sb + 1);
+      if (sb + 1 < super_blocks) prefetch(buf[1], sb_begin + sb + 1);
       run_super_block(buf[0], sb);
       if (sb + 1 < super_blocks) {
-        if (sb + 2 < super_blocks) prefetch_row(buf[0], packed_row, scale_row, zero_row, sb_begin + sb + 2);
+        if (sb + 2 < super_blocks) prefetch(buf[0], sb_begin + sb + 2);
         run_super_block(buf[1], sb + 1);
       }
     }
@@ -207,11 +221,12 @@ __global__ void __launch_bounds__(kThreads, 2)
     tc_fence_after_sync();
     const int quarter = warp & 3;         // TMEM lanes this warp may read
     const int r = quarter * 32 + lane;    // weight row of the tile = TMEM lane
+    const int pair = (warp - 2) >> 2;     // two warps share a quarter: even / odd 32-token chunks
     const uint32_t taddr = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16);
     if (p.slices == 1) {
       if (ok) {
         __half* out = p.y + n0 + r;
-        for (int c0 = 0; c0 < p.tokens; c0 += 32) {
+        for (int c0 = 32 * pair; c0 < p.tokens; c0 += 64) {
           uint32_t v[32];
           tmem_load_32cols(taddr + c0, v);
           tmem_load_wait();
@@ -227,7 +242,7 @@ __global__ void __launch_bounds__(kThreads, 2)
       float* block_partials = p.partials + static_cast<size_t>(n_block) * p.slices * p.M * kRowsW;
       if (ok) {
         float* dst = block_partials + static_cast<size_t>(slice) * p.M * kRowsW + r;
-        for (int c0 = 0; c0 < p.tokens; c0 += 32) {
+        for (int c0 = 32 * pair; c0 < p.tokens; c0 += 64) {
           uint32_t v[32];
           tmem_load_32cols(taddr + c0, v);
           tmem_load_wait();
