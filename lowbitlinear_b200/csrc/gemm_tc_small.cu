@@ -43,7 +43,7 @@ constexpr int kStageBytesW = kRowsW * kBK * 2;      // 16 KB
 constexpr int kStageBytesX = kMaxTokens * kBK * 2;  // 16 KB (BT * 128 bytes are used)
 constexpr int kDequantWarps = 8;  // two threads per weight row, half a group each
 constexpr int kThreads = 32 * (2 + kDequantWarps);
-constexpr int kTmemCols = 128;
+constexpr int kTmemCols = 256;  // accumulators of BT columns each; two CTAs share the 512 of an SM
 constexpr int kBarrierBytes = 256;
 constexpr int kSmemBytes = kStages * (kStageBytesW + kStageBytesX) + kBarrierBytes + 1024;
 constexpr int kStatusSmallWait = 300;
@@ -96,6 +96,10 @@ __global__ void __launch_bounds__(kThreads, 2)
   const int kb_begin = sb_begin * 4;
   const int k_blocks = (sb_end - sb_begin) * 4;
   const uint32_t idesc = instr_desc_f16(kRowsW, static_cast<uint32_t>(p.tokens));
+  // The four MMAs of a k-block go to different accumulators where the tensor memory has room for
+  // them: MMAs on one accumulator run one after the other, and with so few columns each of them
+  // is nearly all latency.  The epilogue adds the accumulators.
+  const int accumulators = p.tokens <= 64 ? 4 : 2;
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < kStages; ++s) {
@@ -144,8 +148,10 @@ __global__ void __launch_bounds__(kThreads, 2)
         const uint32_t x_addr = smem_addr(smem_x + s * kStageBytesX);
 #pragma unroll
         for (int kk = 0; kk < kBK / 16; ++kk) {
-          mma_f16(tmem_base, smem_desc_k_major_sw128(w_addr + kk * 32),
-                  smem_desc_k_major_sw128(x_addr + kk * 32), idesc, (kb | kk) != 0 ? 1u : 0u);
+          const int acc = kk & (accumulators - 1);
+          mma_f16(tmem_base + static_cast<uint32_t>(acc * p.tokens),
+                  smem_desc_k_major_sw128(w_addr + kk * 32), smem_desc_k_major_sw128(x_addr + kk * 32),
+                  idesc, (kb > 0 || kk >= accumulators) ? 1u : 0u);
         }
         mma_commit(&bars->empty[s]);  // frees the stage once these MMAs have read it
       }
@@ -223,13 +229,26 @@ __global__ void __launch_bounds__(kThreads, 2)
     const int r = quarter * 32 + lane;    // weight row of the tile = TMEM lane
     const int pair = (warp - 2) >> 2;     // two warps share a quarter: even / odd 32-token chunks
     const uint32_t taddr = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16);
+    // 32 token columns starting at c0, summed over the accumulators in a fixed order.  (A chunk may
+    // reach past BT into the next accumulator's columns; those values belong to tokens >= M and
+    // are never stored.)
+    auto load_sum = [&](int c0, uint32_t (&v)[32]) {
+      tmem_load_32cols(taddr + c0, v);
+      tmem_load_wait();
+      for (int a = 1; a < accumulators; ++a) {
+        uint32_t w[32];
+        tmem_load_32cols(taddr + a * p.tokens + c0, w);
+        tmem_load_wait();
+#pragma unroll
+        for (int i = 0; i < 32; ++i) v[i] = __float_as_uint(__uint_as_float(v[i]) + __uint_as_float(w[i]));
+      }
+    };
     if (p.slices == 1) {
       if (ok) {
         __half* out = p.y + n0 + r;
         for (int c0 = 32 * pair; c0 < p.tokens; c0 += 64) {
           uint32_t v[32];
-          tmem_load_32cols(taddr + c0, v);
-          tmem_load_wait();
+          load_sum(c0, v);
 #pragma unroll
           for (int i = 0; i < 32; ++i) {
             const int t = c0 + i;
@@ -244,8 +263,7 @@ __global__ void __launch_bounds__(kThreads, 2)
         float* dst = block_partials + static_cast<size_t>(slice) * p.M * kRowsW + r;
         for (int c0 = 32 * pair; c0 < p.tokens; c0 += 64) {
           uint32_t v[32];
-          tmem_load_32cols(taddr + c0, v);
-          tmem_load_wait();
+          load_sum(c0, v);
 #pragma unroll
           for (int i = 0; i < 32; ++i) {
             const int t = c0 + i;
