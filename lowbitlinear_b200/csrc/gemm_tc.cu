@@ -11,18 +11,21 @@
 //
 //   warp 0      one thread issues a 2-D TMA load of the X block (256 rows x 64 columns, 128-byte
 //               swizzle) per stage.
-//   warps 2-9   thread r owns weight row n0 + r.  It prefetches 128 bytes of packed words and the
-//               matching 4 scales / zero points straight from the reference layout into registers
-//               (256 columns of K at a time), dequantises one group per stage and writes the 64
-//               FP16 values as one 128-byte row of the K-major, 128-byte-swizzled B tile, then
-//               fences the async proxy and arrives on the stage's barrier.
+//   warps 2-17  two threads own weight row n0 + r, half a group each.  A thread prefetches its 64
+//               bytes of packed words and the row's 4 scales / zero points straight from the
+//               reference layout into registers (256 columns of K at a time), dequantises its 32
+//               weights of one group per stage into the row's 128 bytes of the K-major,
+//               128-byte-swizzled B tile, then fences the async proxy and arrives on the stage's
+//               barrier.  (Sixteen warps instead of eight: +6 % at M = 2048; the dequantisation
+//               is latency-bound, not throughput-bound.)
 //   warp 1      one thread waits for both halves of a stage and issues 4 (K=16) x 2 (accumulator)
 //               tcgen05.mma instructions, M=128, N=256; tcgen05.commit releases the stage.
-//   warps 2-9   after the last commit: tcgen05.ld of the accumulators (each warp its 32-lane
-//               quarter), FP32 -> FP16, 16-byte stores to Y with the M tail masked.
+//   warps 2-17  after the last commit: tcgen05.ld of the accumulators (each warp a 32-lane
+//               quarter of one accumulator and half of its columns), FP32 -> FP16, 16-byte stores
+//               to Y with the M tail masked.
 //
-// Each weight is dequantised once per 256 rows of X, which keeps the CUDA-core work (about 3.6
-// instructions per weight for the exact policy) under the tensor-core time of the tile.
+// Each weight is dequantised once per 256 rows of X (about 2.6 instructions per weight for the
+// exact policy).
 // Every wait on an mbarrier is bounded; a timeout sets the device status word and the CTA drains.
 // Shapes: N % 256 == 0 and K % 256 == 0; any M >= 1.  No cluster launch, no multicast.
 #include "kernels.h"
@@ -38,7 +41,7 @@ constexpr int kBK = 64;
 constexpr int kStages = 3;
 constexpr int kStageBytesA = kBM * kBK * 2;
 constexpr int kStageBytesB = kBN * kBK * 2;
-constexpr int kDequantWarps = 8;
+constexpr int kDequantWarps = 16;  // two threads per weight row, half a group each
 constexpr int kThreads = 32 * (2 + kDequantWarps);
 constexpr int kTmemCols = 512;
 constexpr int kBarrierBytes = 256;
@@ -146,19 +149,35 @@ __global__ void __launch_bounds__(kThreads, 1)
     }
   } else {
     // ------------------------------- dequantisation warps --------------------------------------
-    const int row = (warp - 2) * 32 + lane;  // row of the B tile, 0..255
+    const int worker = (warp - 2) * 32 + lane;  // 0..511
+    const int row = worker >> 1;                // row of the B tile, 0..255
+    const int half = worker & 1;                // which 32 columns of each group this thread owns
     const size_t n = static_cast<size_t>(n0 + row);
-    const uint32_t* packed_row = p.packed + n * (p.K / 8);
+    const uint32_t* packed_row = p.packed + n * (p.K / 8) + half * 4;
     const float* scale_row = p.scales + n * (p.K / 64);
     const int32_t* zero_row = p.zeros + n * (p.K / 64);
     const uint32_t row_offset = (row >> 3) * 1024 + (row & 7) * 128;
     const uint32_t swz = row & 7;
     const int super_blocks = p.K / 256;
 
-    RowPrefetch buf[2];
-    prefetch_row(buf[0], packed_row, scale_row, zero_row, 0);
+    // Registers <- this thread's packed words and the row's metadata of one super block (256
+    // columns: four groups, four words of each).
+    struct HalfRowPrefetch {
+      uint4 words[4];
+      float4 scale;
+      int4 zero;
+    };
+    auto prefetch = [&](HalfRowPrefetch& buf, int super_block) {
+      const uint32_t* src = packed_row + super_block * 32;
+#pragma unroll
+      for (int j = 0; j < 4; ++j) buf.words[j] = __ldg(reinterpret_cast<const uint4*>(src + j * 8));
+      buf.scale = __ldg(reinterpret_cast<const float4*>(scale_row + super_block * 4));
+      buf.zero = __ldg(reinterpret_cast<const int4*>(zero_row + super_block * 4));
+    };
+    HalfRowPrefetch buf[2];
+    prefetch(buf[0], 0);
 
-    auto run_super_block = [&](const RowPrefetch& cur, int sb) {
+    auto run_super_block = [&](const HalfRowPrefetch& cur, int sb) {
       const float sc[4] = {cur.scale.x, cur.scale.y, cur.scale.z, cur.scale.w};
       const int zp[4] = {cur.zero.x, cur.zero.y, cur.zero.z, cur.zero.w};
 #pragma unroll
@@ -172,13 +191,11 @@ __global__ void __launch_bounds__(kThreads, 1)
         }
         const GroupConstants group = group_constants(sc[j], zp[j]);
         uint8_t* dst = smem_b + s * kStageBytesB + row_offset;
-        const uint4 wa = cur.words[2 * j];
-        const uint4 wb = cur.words[2 * j + 1];
-        const uint32_t w[8] = {wa.x, wa.y, wa.z, wa.w, wb.x, wb.y, wb.z, wb.w};
+        const uint32_t w[4] = {cur.words[j].x, cur.words[j].y, cur.words[j].z, cur.words[j].w};
 #pragma unroll
-        for (int c = 0; c < 8; ++c) {
+        for (int c = 0; c < 4; ++c) {
           const uint4 out = dequant_word(w[c], group);
-          *reinterpret_cast<uint4*>(dst + ((static_cast<uint32_t>(c) ^ swz) << 4)) = out;
+          *reinterpret_cast<uint4*>(dst + ((static_cast<uint32_t>(half * 4 + c) ^ swz) << 4)) = out;
         }
         fence_async_proxy();  // generic-proxy writes -> visible to the tensor core's reads
         __syncwarp();
@@ -187,10 +204,10 @@ __global__ void __launch_bounds__(kThreads, 1)
     };
 
     for (int sb = 0; sb < super_blocks; sb += 2) {
-      if (sb + 1 < super_blocks) prefetch_row(buf[1], packed_row, scale_row, zero_row, sb + 1);
+      if (sb + 1 < super_blocks) prefetch(buf[1], sb + 1);
       run_super_block(buf[0], sb);
       if (sb + 1 < super_blocks) {
-        if (sb + 2 < super_blocks) prefetch_row(buf[0], packed_row, scale_row, zero_row, sb + 2);
+        if (sb + 2 < super_blocks) prefetch(buf[0], sb + 2);
         run_super_block(buf[1], sb + 1);
       }
     }
@@ -199,12 +216,13 @@ __global__ void __launch_bounds__(kThreads, 1)
     const bool ok = mbar_wait_bounded(&bars->acc_full, 0, abort_flag, p.status, kStatusGemmWait + 5);
     tc_fence_after_sync();
     const int quarter = warp & 3;        // TMEM lanes this warp may read
-    const int h = (warp - 2) >> 2;       // accumulator handled by this warp
+    const int h = ((warp - 2) >> 2) & 1;  // accumulator handled by this warp
+    const int column_half = (warp - 2) >> 3;  // two warps share a quarter of an accumulator
     if (ok && h < halves) {
       const int m = m0 + h * 128 + quarter * 32 + lane;
       __half* out_row = p.y + static_cast<size_t>(m < p.M ? m : 0) * p.N + n0;
       const uint32_t taddr = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) + h * kBN;
-      for (int c0 = 0; c0 < kBN; c0 += 32) {
+      for (int c0 = column_half * (kBN / 2); c0 < (column_half + 1) * (kBN / 2); c0 += 32) {
         uint32_t v[32];
         tmem_load_32cols(taddr + c0, v);
         tmem_load_wait();
