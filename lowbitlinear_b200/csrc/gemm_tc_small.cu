@@ -159,68 +159,10 @@ __global__ void __launch_bounds__(kThreads, 2)
     }
   } else {
     // ------------------------------- dequantisation warps --------------------------------------
-    const int worker = (warp - 2) * 32 + lane;  // 0..255
-    const int row = worker >> 1;                // row of the weight tile, 0..127
-    const int half = worker & 1;                // which 32 columns of each group this thread owns
-    const size_t n = static_cast<size_t>(n0 + row);
-    const uint32_t* packed_row = p.packed + n * (p.K / 8) + half * 4;
-    const float* scale_row = p.scales + n * (p.K / 64);
-    const int32_t* zero_row = p.zeros + n * (p.K / 64);
-    const uint32_t row_offset = (row >> 3) * 1024 + (row & 7) * 128;
-    const uint32_t swz = row & 7;
-
-    // Registers <- this thread's packed words and the row's metadata of one super block (256
-    // columns: four groups, four words of each).
-    struct HalfRowPrefetch {
-      uint4 words[4];
-      float4 scale;
-      int4 zero;
-    };
-    auto prefetch = [&](HalfRowPrefetch& buf, int super_block) {
-      const uint32_t* src = packed_row + super_block * 32;
-#pragma unroll
-      for (int j = 0; j < 4; ++j) buf.words[j] = __ldg(reinterpret_cast<const uint4*>(src + j * 8));
-      buf.scale = __ldg(reinterpret_cast<const float4*>(scale_row + super_block * 4));
-      buf.zero = __ldg(reinterpret_cast<const int4*>(zero_row + super_block * 4));
-    };
-    HalfRowPrefetch buf[2];
-    prefetch(buf[0], sb_begin);
-
-    // `sb` counts this CTA's super blocks from 0; the data come from super block sb_begin + sb.
-    const int super_blocks = sb_end - sb_begin;
-    auto run_super_block = [&](const HalfRowPrefetch& cur, int sb) {
-      const float sc[4] = {cur.scale.x, cur.scale.y, cur.scale.z, cur.scale.w};
-      const int zp[4] = {cur.zero.x, cur.zero.y, cur.zero.z, cur.zero.w};
-#pragma unroll
-      for (int j = 0; j < 4; ++j) {
-        const int kb = sb * 4 + j;
-        const int s = kb % kStages;
-        const int round = kb / kStages;
-        if (round > 0) {
-          mbar_wait_bounded(&bars->empty[s], (round - 1) & 1, abort_flag, p.status, kStatusSmallWait + 4);
-        }
-        const GroupConstants group = group_constants(sc[j], zp[j]);
-        uint8_t* dst = smem_w + s * kStageBytesW + row_offset;
-        const uint32_t w[4] = {cur.words[j].x, cur.words[j].y, cur.words[j].z, cur.words[j].w};
-#pragma unroll
-        for (int c = 0; c < 4; ++c) {
-          const uint4 out = dequant_word(w[c], group);
-          *reinterpret_cast<uint4*>(dst + ((static_cast<uint32_t>(half * 4 + c) ^ swz) << 4)) = out;
-        }
-        fence_async_proxy();  // generic-proxy writes -> visible to the tensor core's reads
-        __syncwarp();
-        if (lane == 0) mbar_arrive(&bars->w_full[s]);
-      }
-    };
-
-    for (int sb = 0; sb < super_blocks; sb += 2) {
-      if (sb + 1 < super_blocks) prefetch(buf[1], sb_begin + sb + 1);
-      run_super_block(buf[0], sb);
-      if (sb + 1 < super_blocks) {
-        if (sb + 2 < super_blocks) prefetch(buf[0], sb_begin + sb + 2);
-        run_super_block(buf[1], sb + 1);
-      }
-    }
+    dequantise_rows<kStages, kStageBytesW>(p.packed, p.scales, p.zeros, p.K, static_cast<size_t>(n0),
+                                           (warp - 2) * 32 + lane, sb_begin, sb_end, smem_w,
+                                           bars->w_full, bars->empty, abort_flag, p.status,
+                                           kStatusSmallWait + 4);
 
     // ------------------------------- epilogue ---------------------------------------------------
     const bool ok = mbar_wait_bounded(&bars->acc_full, 0, abort_flag, p.status, kStatusSmallWait + 5);

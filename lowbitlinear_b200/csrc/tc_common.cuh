@@ -119,20 +119,79 @@ __device__ __forceinline__ uint4 dequant_word(uint32_t word, const GroupConstant
   return out;
 }
 
-struct RowPrefetch {
-  uint4 words[8];  // 32 packed words = 256 columns
-  float4 scale;    // 4 groups
+// ---- the dequantisation worker shared by the tensor-core kernels ------------------------------
+// Two threads own one weight row of the K-major, 128-byte-swizzled tile, half a group (32 columns)
+// each.  A thread keeps the packed words of two super blocks (256 columns: four groups, four words
+// of each) and the row's metadata in registers, one being consumed while the next is in flight.
+struct HalfRowPrefetch {
+  uint4 words[4];
+  float4 scale;
   int4 zero;
 };
 
-__device__ __forceinline__ void prefetch_row(RowPrefetch& buf, const uint32_t* packed_row,
-                                             const float* scale_row, const int32_t* zero_row,
-                                             int super_block) {
-  const uint4* src = reinterpret_cast<const uint4*>(packed_row + super_block * 32);
+// Walks super blocks [sb_begin, sb_end) of weight row `n`.  For its j-th k-block (one group) it
+// waits until ring stage j % kStages is free, writes its 32 dequantised weights into the stage's
+// tile at `tiles + stage * kStageBytes`, fences the async proxy and arrives (one arrival per warp)
+// on full[stage].  `worker` is the thread's index among the dequantisation threads (row = worker
+// / 2, half = worker % 2); `status_code` is reported if a wait on `empty` expires.
+template <int kStages, int kStageBytes>
+__device__ __forceinline__ void dequantise_rows(const uint32_t* packed, const float* scales,
+                                                const int32_t* zeros, int K, size_t n0, int worker,
+                                                int sb_begin, int sb_end, uint8_t* tiles,
+                                                uint64_t* full, uint64_t* empty,
+                                                volatile int* abort_flag, int* status, int status_code) {
+  const int lane = threadIdx.x & 31;
+  const int row = worker >> 1;
+  const int half = worker & 1;
+  const size_t n = n0 + row;
+  const uint32_t* packed_row = packed + n * (K / 8) + half * 4;
+  const float* scale_row = scales + n * (K / 64);
+  const int32_t* zero_row = zeros + n * (K / 64);
+  const uint32_t row_offset = (row >> 3) * 1024 + (row & 7) * 128;
+  const uint32_t swz = row & 7;
+
+  auto prefetch = [&](HalfRowPrefetch& buf, int super_block) {
+    const uint32_t* src = packed_row + super_block * 32;
 #pragma unroll
-  for (int i = 0; i < 8; ++i) buf.words[i] = __ldg(src + i);
-  buf.scale = __ldg(reinterpret_cast<const float4*>(scale_row + super_block * 4));
-  buf.zero = __ldg(reinterpret_cast<const int4*>(zero_row + super_block * 4));
+    for (int j = 0; j < 4; ++j) buf.words[j] = __ldg(reinterpret_cast<const uint4*>(src + j * 8));
+    buf.scale = __ldg(reinterpret_cast<const float4*>(scale_row + super_block * 4));
+    buf.zero = __ldg(reinterpret_cast<const int4*>(zero_row + super_block * 4));
+  };
+  // `sb` counts this CTA's super blocks from 0; the data come from super block sb_begin + sb.
+  auto run_super_block = [&](const HalfRowPrefetch& cur, int sb) {
+    const float sc[4] = {cur.scale.x, cur.scale.y, cur.scale.z, cur.scale.w};
+    const int zp[4] = {cur.zero.x, cur.zero.y, cur.zero.z, cur.zero.w};
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      const int kb = sb * 4 + j;
+      const int s = kb % kStages;
+      const int round = kb / kStages;
+      if (round > 0) mbar_wait_bounded(&empty[s], (round - 1) & 1, abort_flag, status, status_code);
+      const GroupConstants group = group_constants(sc[j], zp[j]);
+      uint8_t* dst = tiles + s * kStageBytes + row_offset;
+      const uint32_t w[4] = {cur.words[j].x, cur.words[j].y, cur.words[j].z, cur.words[j].w};
+#pragma unroll
+      for (int c = 0; c < 4; ++c) {
+        const uint4 out = dequant_word(w[c], group);
+        *reinterpret_cast<uint4*>(dst + ((static_cast<uint32_t>(half * 4 + c) ^ swz) << 4)) = out;
+      }
+      fence_async_proxy();  // generic-proxy writes -> visible to the tensor core's reads
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&full[s]);
+    }
+  };
+
+  const int super_blocks = sb_end - sb_begin;
+  HalfRowPrefetch buf[2];
+  prefetch(buf[0], sb_begin);
+  for (int sb = 0; sb < super_blocks; sb += 2) {
+    if (sb + 1 < super_blocks) prefetch(buf[1], sb_begin + sb + 1);
+    run_super_block(buf[0], sb);
+    if (sb + 1 < super_blocks) {
+      if (sb + 2 < super_blocks) prefetch(buf[0], sb_begin + sb + 2);
+      run_super_block(buf[1], sb + 1);
+    }
+  }
 }
 
 }  // namespace
