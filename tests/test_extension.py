@@ -225,3 +225,20 @@ assert actual.device == x.device
 assert torch.equal(actual, torch.full_like(actual, 256.))
 """
     subprocess.run([sys.executable, "-c", code, op_name], check=True, timeout=180, cwd=ROOT)
+
+
+def test_a_library_built_from_older_sources_is_reported(monkeypatch):
+    """The loader compares the recorded build fingerprint with the present sources before it
+    touches the shared object (a loaded library stays mapped for the life of the process)."""
+    from lowbitlinear_b200 import _extension, _fingerprint
+
+    recorded = _fingerprint.recorded_build()
+    if recorded is None:
+        pytest.skip("no build record in this tree")
+    fingerprint, flags, defines = recorded
+    assert _fingerprint.source_fingerprint(flags, defines) == fingerprint
+    assert not _extension._is_out_of_date()
+    monkeypatch.setattr(_fingerprint, "recorded_build", lambda: ("0" * 64, flags, defines))
+    assert _extension._is_out_of_date()
+    monkeypatch.setattr(_fingerprint, "recorded_build", lambda: None)
+    assert not _extension._is_out_of_date()
