@@ -3,7 +3,7 @@
 Run once, in a container that has the reference checked out (it is not needed afterwards and
 does not exist on the GPU machines):
 
-    python tests/golden/make_golden.py --reference /root/reference
+    python tests/golden/make_golden.py --reference <checkout of NanjinLin/LowBitLinear>
 
 The reference package (NanjinLin/LowBitLinear, ``lowbitlinear/``) is imported from that path
 and nothing of it is copied: its ``quantize_int4`` / ``pack_int4`` / ``linear_int4_reference``
@@ -64,7 +64,7 @@ def sha(t):
 
 def main():
     parser = argparse.ArgumentParser()
-    parser.add_argument("--reference", default="/root/reference")
+    parser.add_argument("--reference", required=True, help="path of the reference checkout")
     args = parser.parse_args()
     sys.path.insert(0, args.reference)
     import lowbitlinear  # the reference package
