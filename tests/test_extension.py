@@ -94,6 +94,10 @@ def test_dispatcher_choices_and_scratch_sizes():
         assert ws(1, 4096, 4096, _ops.PATH_AUTO) == 0
         assert ws(1, 512, 4096, _ops.PATH_AUTO) == 64 * 1024 + 4 * 512 * 4
         assert ws(2048, 24576, 4096, _ops.PATH_AUTO) == 0
+        # small-M tensor-core GEMM: counters + one FP32 partial tile [M, 128] per row block and
+        # slice of K; 32 row blocks are cut 8 ways, 192 row blocks 3 ways (waves of 2 * 148 CTAs)
+        assert ws(16, 4096, 4096, _ops.PATH_AUTO) == 64 * 1024 + 32 * 8 * 16 * 128 * 4
+        assert ws(16, 24576, 4096, _ops.PATH_AUTO) == 64 * 1024 + 192 * 3 * 16 * 128 * 4
     finally:
         for k, v in env_backup.items():
             if v is not None:
