@@ -220,7 +220,7 @@ int run_linear(const void* X, const int32_t* packed_w, const float* scales, cons
         return fail(LBL_ERR_UNSUPPORTED, "small-M tensor-core GEMM cannot serve M=%lld N=%lld K=%lld (needs M <= 128, N %% 128 == 0, K %% 256 == 0)", (long long)M, (long long)N, (long long)K);
       }
       err = lbl::launch_gemm_tc_small(prob, info.status_word, cu_stream, workspace, workspace_bytes,
-                                      info.sm_count);
+                                      info.sm_count, (flags & LBL_FLAG_PDL) != 0);
       break;
     }
     default:

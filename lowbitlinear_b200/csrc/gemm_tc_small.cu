@@ -119,10 +119,15 @@ __global__ void __launch_bounds__(kThreads, 2)
   __syncthreads();
   tc_fence_after_sync();
   const uint32_t tmem_base = *reinterpret_cast<volatile uint32_t*>(&bars->tmem_base);
+  // Programmatic dependent launch (no-ops without it): the next kernel in the stream may start
+  // as soon as it finds room; in this one only the activations, the outputs and the scratch
+  // depend on the kernel before, so the weights are fetched and dequantised without waiting.
+  pdl_allow_next_kernel();
 
   if (warp == 0) {
     // ------------------------------- TMA producer (X blocks) ---------------------------------
     if (lane == 0) {
+      pdl_wait_for_previous_kernel();
       for (int kb = 0; kb < k_blocks; ++kb) {
         const int s = kb % kStages;
         const int round = kb / kStages;
@@ -167,6 +172,7 @@ __global__ void __launch_bounds__(kThreads, 2)
     // ------------------------------- epilogue ---------------------------------------------------
     const bool ok = mbar_wait_bounded(&bars->acc_full, 0, abort_flag, p.status, kStatusSmallWait + 5);
     tc_fence_after_sync();
+    pdl_wait_for_previous_kernel();  // before the first write to Y or the scratch
     const int quarter = warp & 3;         // TMEM lanes this warp may read
     const int r = quarter * 32 + lane;    // weight row of the tile = TMEM lane
     const int pair = (warp - 2) >> 2;     // two warps share a quarter: even / odd 32-token chunks
@@ -307,7 +313,7 @@ size_t gemm_tc_small_workspace_bytes(int64_t M, int64_t N, int64_t K, int sm_cou
 }
 
 cudaError_t launch_gemm_tc_small(const Problem& p, int* status_word, cudaStream_t stream, void* workspace,
-                                 size_t workspace_bytes, int sm_count) {
+                                 size_t workspace_bytes, int sm_count, bool pdl) {
   const int tokens = static_cast<int>((p.M + 15) / 16 * 16);
   CUtensorMap tmap;
   const uint64_t dims[2] = {static_cast<uint64_t>(p.K), static_cast<uint64_t>(p.M)};
@@ -351,8 +357,17 @@ cudaError_t launch_gemm_tc_small(const Problem& p, int* status_word, cudaStream_
     sp.partials = reinterpret_cast<float*>(static_cast<char*>(workspace) + kSkinnyTicketBytes);
   }
   const unsigned grid = static_cast<unsigned>(sp.n_blocks) * static_cast<unsigned>(sp.slices);
-  w4a16_gemm_tc_small_kernel<<<grid, kThreads, kSmemBytes, stream>>>(tmap, sp);
-  return cudaGetLastError();
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3(grid);
+  cfg.blockDim = dim3(kThreads);
+  cfg.dynamicSmemBytes = kSmemBytes;
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = pdl ? 1 : 0;
+  return cudaLaunchKernelEx(&cfg, w4a16_gemm_tc_small_kernel, tmap, sp);
 }
 
 }  // namespace lbl

@@ -88,6 +88,6 @@ bool gemm_tc_small_supports(int64_t M, int64_t N, int64_t K);
 // arrival counters, then FP32 partial tiles.  Optional: without it one CTA walks the whole of K.
 size_t gemm_tc_small_workspace_bytes(int64_t M, int64_t N, int64_t K, int sm_count);
 cudaError_t launch_gemm_tc_small(const Problem& p, int* status_word, cudaStream_t stream, void* workspace,
-                                 size_t workspace_bytes, int sm_count);
+                                 size_t workspace_bytes, int sm_count, bool pdl);
 
 }  // namespace lbl
