@@ -64,9 +64,11 @@ const char* lbl_last_error(void);
  * (FP32 dequantisation) and 1 for the any-shape operator. */
 int lbl_w4a16_select_path(int64_t M, int64_t N, int64_t K, int op);
 
-/* Bytes of scratch the given path (or LBL_PATH_AUTO) needs for this problem; 0 if none.
- * The scratch starts with a fixed 64 KiB region of arrival counters (one per 16-row tile),
- * followed by the split-K partial sums.  The buffer must be zero before the first call that
+/* Bytes of scratch the given path (or LBL_PATH_AUTO) wants for this problem; 0 if none.
+ * Split-K GEMV requires it (LBL_ERR_WORKSPACE otherwise); LBL_PATH_GEMM_TC_SMALL uses it to cut K
+ * into slices and runs one CTA per 128 output columns without it.
+ * The scratch starts with a fixed 64 KiB region of arrival counters (one per 16-row tile or
+ * 128-column block), followed by the FP32 partial sums.  The buffer must be zero before the first call that
  * uses it (lbl_w4a16_workspace_init); every call leaves the counters zero again and the
  * counter region never moves, so one buffer can be reused by successive calls, of any
  * shape, on the same stream.  Calls that overlap on the GPU need separate buffers. */
