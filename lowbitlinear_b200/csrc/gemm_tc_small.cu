@@ -10,8 +10,9 @@
 //
 //   D[128 weight rows, BT tokens] = W_tile[128, K slice] . X[BT, K slice]^T,   BT = M rounded up to 16
 //
-// with one accumulator of BT columns in tensor memory; two CTAs share an SM.  K is cut into slices
-// (whole super blocks of 256 columns) until about two CTAs per SM exist; slices of one row block
+// with two or four accumulators of BT columns in tensor memory (the MMAs of a k-block alternate
+// between them, the epilogue adds them); two CTAs share an SM.  K is cut into slices (whole super
+// blocks of 256 columns) until the waves of two CTAs per SM are about full; slices of one row block
 // meet as FP32 partial tiles in the scratch, and the CTA that draws the block's last ticket adds
 // them in slice order and writes FP16 (same protocol as the split-K GEMV: bit-reproducible).
 //
@@ -24,6 +25,8 @@
 //   warps 2-9   epilogue: tcgen05.ld of the accumulator, lane = weight row, so that for each token
 //               a warp stores 32 neighbouring outputs.
 //
+// With programmatic dependent launch the weights are fetched and dequantised before the previous
+// kernel in the stream has finished; the X loads, the outputs and the scratch wait for it.
 // Every wait on an mbarrier is bounded.  Shapes: N % 128 == 0, K % 256 == 0, 1 <= M <= 128.
 // No cluster launch, no multicast.
 #include "kernels.h"
