@@ -148,6 +148,45 @@ int lbl_w4a16_gemv_allreduce(const void* x, const int32_t* packed_w, const float
                              void* workspace, size_t workspace_bytes, unsigned flags, int device,
                              void* stream);
 
+/* ---- Grouped decode GEMV: many independent problems, one launch ------------------------------
+ * The reference launches one kernel per linear (csrc/w4a16_gemv_warp_vec.cu:171-187); at decode
+ * sizes the fixed cost of a launch rivals the time its weights need to cross the memory bus.  A
+ * group describes a list of problems with M <= 2 once -- lbl_w4a16_group_create builds their
+ * tensor maps and cuts the byte stream of all weights into one contiguous share per persistent
+ * CTA, in device memory it allocates (a synchronous set-up call) -- and lbl_w4a16_group_run then
+ * computes all of them in ONE launch on `stream`, reading x and writing y of every problem as
+ * given at creation (static buffers, which is also what CUDA-graph capture wants).
+ *  - The problems must be independent: no problem's x may be another problem's y.
+ *  - Per problem: 1 <= M <= 2, K % 256 == 0, M * K <= 32768, all tensors 16-byte aligned;
+ *    FP32-scale numerics of lbl_w4a16_gemv.
+ *  - Tensor parallel: create the group on every rank with that rank's shards, pass the exchange
+ *    buffers of all ranks (lbl_peer_buffer_*) and set `reduce` on the K-split problems; run then
+ *    launches a second kernel that sums those problems' FP32 partial outputs over the ranks with
+ *    plain peer loads over NVLink (bounded wait for the peers; NaN outputs and a non-zero
+ *    lbl_device_status if a peer never shows up) and writes the same FP16 y on every rank.  All
+ *    ranks must run their groups the same number of times.  With world == 1 pass rank 0,
+ *    world 1, buffers NULL.
+ * A group may be run any number of times, also inside a stream capture; destroy it after the
+ * last run has finished. */
+typedef struct lbl_w4a16_problem {
+  const void* x;            /* [M, K] FP16 */
+  const int32_t* packed_w;  /* [N, K/8] */
+  const float* scales;      /* [N, K/64] */
+  const int32_t* zeros;     /* [N, K/64] */
+  void* y;                  /* [M, N] FP16 */
+  int64_t M, N, K;
+  int32_t reduce;           /* 1: K-split shard, y = sum over the ranks (needs the exchange) */
+  int32_t reserved;
+} lbl_w4a16_problem;
+typedef struct lbl_w4a16_group lbl_w4a16_group;
+int lbl_w4a16_group_create(const lbl_w4a16_problem* problems, int count, int rank, int world,
+                           void* const* buffers, int64_t buffer_capacity_n, int device,
+                           lbl_w4a16_group** group);
+int lbl_w4a16_group_run(lbl_w4a16_group* group, unsigned flags, void* stream);
+/* Sum over the problems of N K / 2 + 8 N K / 64 + 2 M K + 2 M N (what a benchmark divides by). */
+int64_t lbl_w4a16_group_algorithmic_bytes(const lbl_w4a16_group* group);
+int lbl_w4a16_group_destroy(lbl_w4a16_group* group);
+
 /* ---- Quantiser -----------------------------------------------------------------------------
  * Replaces QuantizedLinear.from_float's quantize_int4 + pack_int4 pair
  * (lowbitlinear/linear.py:55-76, lowbitlinear/quantization.py:33-86 and :112-141) for weights

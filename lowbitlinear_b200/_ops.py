@@ -32,6 +32,16 @@ GEMV_SCHEMA = (
 )
 GEMM_SCHEMA = "gemm(Tensor X, Tensor packed_w, Tensor scales, Tensor zeros) -> Tensor"
 
+
+
+class GroupProblem(ctypes.Structure):
+    """``lbl_w4a16_problem`` of the C ABI."""
+    _fields_ = [("x", ctypes.c_void_p), ("packed_w", ctypes.c_void_p), ("scales", ctypes.c_void_p),
+                ("zeros", ctypes.c_void_p), ("y", ctypes.c_void_p), ("M", ctypes.c_int64),
+                ("N", ctypes.c_int64), ("K", ctypes.c_int64), ("reduce", ctypes.c_int32),
+                ("reserved", ctypes.c_int32)]
+
+
 _lib = None
 _registered = []  # keeps the torch.library.Library objects alive
 ERR_WORKSPACE = -3  # LBL_ERR_WORKSPACE
@@ -84,6 +94,19 @@ def bind(path):
     lib.lbl_w4a16_quantize.argtypes = [p, i32, i64, i64, i32, p, p, p, i32, p]
     lib.lbl_w4a16_dequantize.restype = i32
     lib.lbl_w4a16_dequantize.argtypes = [p, p, p, p, i32, i64, i64, i32, i32, p]
+    lib.lbl_w4a16_group_create.restype = i32
+    lib.lbl_w4a16_group_create.argtypes = [ctypes.POINTER(GroupProblem), i32, i32, i32, ctypes.POINTER(p), i64, i32,
+                                           ctypes.POINTER(p)]
+    lib.lbl_w4a16_group_run.restype = i32
+    lib.lbl_w4a16_group_run.argtypes = [p, u32, p]
+    lib.lbl_w4a16_group_algorithmic_bytes.restype = i64
+    lib.lbl_w4a16_group_algorithmic_bytes.argtypes = [p]
+    lib.lbl_w4a16_group_destroy.restype = i32
+    lib.lbl_w4a16_group_destroy.argtypes = [p]
+    lib.lbl_w4a16_gemv_noalloc.restype = i32
+    lib.lbl_w4a16_gemv_noalloc.argtypes = [p, p, p, p, p, i64, i64, i32, u32, i32, p]
+    lib.lbl_w4a16_gemv_noalloc_scratch_bytes.restype = sz
+    lib.lbl_w4a16_gemv_noalloc_scratch_bytes.argtypes = []
     _lib = lib
     return lib
 
@@ -254,10 +277,12 @@ def linear_forced(X, packed_w, scales, zeros, path, op=1, flags=None):
     return Y, taken.value
 
 
-def linear_out(X, packed_w, scales, zeros, out, op=None):
+def linear_out(X, packed_w, scales, zeros, out, op=None, workspace=None):
     """Dispatcher call that writes into a caller-provided ``out`` ``[M, N]`` (FP16, contiguous,
     16-byte aligned) instead of allocating: what a CUDA-graph runner with static buffers needs.
-    ``op`` defaults to the operator ``QuantizedLinear.forward`` would pick."""
+    ``op`` defaults to the operator ``QuantizedLinear.forward`` would pick.  ``workspace`` is a
+    zero-initialised uint8 CUDA tensor the caller owns (at least ``lbl_w4a16_workspace_bytes``);
+    without it the per-stream cached scratch is used."""
     m, k = X.shape
     n = packed_w.size(0)
     if op is None:
@@ -265,9 +290,12 @@ def linear_out(X, packed_w, scales, zeros, out, op=None):
     stream = _raw_stream(X.device)
     px, pw, ps, pz, py, index = (X.data_ptr(), packed_w.data_ptr(), scales.data_ptr(), zeros.data_ptr(),
                                  out.data_ptr(), X.device.index)
-    _run(X.device, stream, m, n, k, PATH_AUTO,
-         lambda ws, ws_bytes: _lib.lbl_w4a16_linear(px, pw, ps, pz, py, m, n, k, op, PATH_AUTO, ws,
-                                                    ws_bytes, _flags, index, stream, None))
+    call = lambda ws, ws_bytes: _lib.lbl_w4a16_linear(px, pw, ps, pz, py, m, n, k, op, PATH_AUTO, ws,
+                                                      ws_bytes, _flags, index, stream, None)
+    if workspace is not None:
+        _check(call(workspace.data_ptr(), workspace.numel()))
+    else:
+        _run(X.device, stream, m, n, k, PATH_AUTO, call)
     return out
 
 
@@ -284,6 +312,71 @@ def gemv_allreduce(x, packed_w, scales, zeros, exchange):
              64, exchange.rank, exchange.world, exchange.pointers, exchange.capacity_n, ws, ws_bytes,
              _flags, x.device.index, stream))
     return y
+
+
+class LinearGroup:
+    """A list of independent decode linears (M <= 2) that run as ONE persistent launch.
+
+    ``problems`` is a sequence of ``(x, packed_w, scales, zeros, y)`` or
+    ``(x, packed_w, scales, zeros, y, reduce)`` tuples of CUDA tensors on one device: ``x``
+    ``[M, K]`` FP16 and ``y`` ``[M, N]`` FP16 are static buffers that every ``run()`` reads and
+    writes.  With an ``exchange`` (``tensor_parallel.PeerExchange``) the problems flagged
+    ``reduce`` are K-split shards whose outputs are summed over the ranks by a second kernel over
+    NVLink peer memory; every rank must then call ``run()`` the same number of times.
+    The reference launches one kernel per linear (``csrc/w4a16_gemv_warp_vec.cu:171-187``)."""
+
+    def __init__(self, problems, exchange=None):
+        problems = [tuple(q) for q in problems]
+        if not problems:
+            raise ValueError("no problems")
+        self.device = problems[0][0].device
+        array = (GroupProblem * len(problems))()
+        self._keep = []
+        for slot, q in zip(array, problems):
+            x, packed_w, scales, zeros, y = q[:5]
+            reduce = bool(q[5]) if len(q) > 5 else False
+            _require(all(t.is_cuda and t.device == self.device and t.is_contiguous()
+                         for t in (x, packed_w, scales, zeros, y)),
+                     "all tensors of a group must be contiguous CUDA tensors on one device")
+            _require(x.dtype == torch.float16 and y.dtype == torch.float16 and packed_w.dtype == torch.int32
+                     and scales.dtype == torch.float32 and zeros.dtype == torch.int32, "wrong dtype in a group problem")
+            m, k = x.shape
+            n = packed_w.size(0)
+            _require(tuple(packed_w.shape) == (n, k // 8) and tuple(scales.shape) == (n, k // 64)
+                     and zeros.shape == scales.shape and tuple(y.shape) == (m, n), "wrong shape in a group problem")
+            slot.x, slot.packed_w, slot.scales, slot.zeros, slot.y = (x.data_ptr(), packed_w.data_ptr(),
+                                                                      scales.data_ptr(), zeros.data_ptr(), y.data_ptr())
+            slot.M, slot.N, slot.K, slot.reduce, slot.reserved = m, n, k, int(reduce), 0
+            self._keep.append((x, packed_w, scales, zeros, y))
+        self.exchange = exchange
+        handle = ctypes.c_void_p()
+        if exchange is not None:
+            rc = _lib.lbl_w4a16_group_create(array, len(problems), exchange.rank, exchange.world,
+                                             exchange.pointers, exchange.capacity_n, self.device.index,
+                                             ctypes.byref(handle))
+        else:
+            rc = _lib.lbl_w4a16_group_create(array, len(problems), 0, 1, None, 0, self.device.index,
+                                             ctypes.byref(handle))
+        _check(rc)
+        self._handle = handle
+        self.count = len(problems)
+        self.algorithmic_bytes = _lib.lbl_w4a16_group_algorithmic_bytes(handle)
+
+    def run(self):
+        """Launch on the current stream of the group's device (asynchronous)."""
+        _check(_lib.lbl_w4a16_group_run(self._handle, _flags, _raw_stream(self.device)))
+
+    def close(self):
+        """Free the plan; call it after the last run has finished."""
+        if self._handle is not None:
+            _lib.lbl_w4a16_group_destroy(self._handle)
+            self._handle = None
+
+    def __del__(self):
+        try:
+            self.close()
+        except Exception:  # noqa: BLE001  (interpreter shutdown)
+            pass
 
 
 def quantize_pack(weight, group_size=64):

@@ -9,6 +9,7 @@
 #include <cstdlib>
 #include <cstring>
 #include <mutex>
+#include <vector>
 
 namespace {
 
@@ -87,26 +88,21 @@ int device_info(int device, DeviceInfo* out) {
 
 bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
 
+// The one runtime knob: LBL_FORCE_PATH=<path code> makes every dispatcher call without an explicit
+// path take that kernel (crossover measurements).  Read once, when the library is first used.
 int forced_path_from_env() {
-  const char* v = std::getenv("LBL_FORCE_PATH");
-  if (v == nullptr || *v == '\0') return LBL_PATH_AUTO;
-  return std::atoi(v);
+  static const int forced = [] {
+    const char* v = std::getenv("LBL_FORCE_PATH");
+    return (v == nullptr || *v == '\0') ? LBL_PATH_AUTO : std::atoi(v);
+  }();
+  return forced;
 }
 
-// Crossover between the streaming kernel and the tensor-core GEMM.
-int tc_min_m() {
-  const char* v = std::getenv("LBL_TC_MIN_M");
-  if (v == nullptr || *v == '\0') return 17;
-  return std::atoi(v);
-}
-
-// From this M on, shapes the small-M tensor-core GEMM can serve go to it instead of the streaming
-// kernel (which it overtakes as the rows of activations fill more MMA columns).
-int tc_small_min_m() {
-  const char* v = std::getenv("LBL_TC_SMALL_MIN_M");
-  if (v == nullptr || *v == '\0') return 9;
-  return std::atoi(v);
-}
+// Crossover thresholds (measured on B200).  From kTcSmallMinM rows of activations on, shapes the
+// small-M tensor-core GEMM can serve go to it instead of the streaming kernel; from kTcMinM on
+// the large tensor-core GEMM takes what the small one cannot.
+constexpr int kTcMinM = 17;
+constexpr int kTcSmallMinM = 9;
 
 int select_path(int64_t M, int64_t N, int64_t K, int op, int sm_count) {
   (void)op;
@@ -118,10 +114,10 @@ int select_path(int64_t M, int64_t N, int64_t K, int op, int sm_count) {
   // Measured (B200): with 9..128 rows of activations the small-M tensor-core GEMM wins wherever
   // the 256-wide tiles of the large one cannot fill the SMs (N < 16384), and up to M = 32 beyond.
   const bool wide = N >= 16384;
-  if (M >= tc_small_min_m() && lbl::gemm_tc_small_supports(M, N, K) && (!wide || M <= 32 || !tc_ok)) {
+  if (M >= kTcSmallMinM && lbl::gemm_tc_small_supports(M, N, K) && (!wide || M <= 32 || !tc_ok)) {
     return LBL_PATH_GEMM_TC_SMALL;
   }
-  if (tc_ok && (M >= tc_min_m() || (wide && M >= 9) || !skinny_ok)) return LBL_PATH_GEMM_TC;
+  if (tc_ok && (M >= kTcMinM || (wide && M >= 9) || !skinny_ok)) return LBL_PATH_GEMM_TC;
   if (skinny_ok) {
     lbl::SkinnyPlan plan;
     if (lbl::skinny_make_plan(M, N, K, -1, sm_count, &plan)) {
@@ -137,6 +133,10 @@ int run_linear(const void* X, const int32_t* packed_w, const float* scales, cons
   if (M < 0 || N < 0 || K < 0) return fail(LBL_ERR_INVALID, "negative dimension (M=%lld N=%lld K=%lld)", (long long)M, (long long)N, (long long)K);
   if (path_taken != nullptr) *path_taken = LBL_PATH_AUTO;
   if (M == 0 || N == 0) return LBL_OK;  // empty output
+  // Every path that touches the scratch does so with 16-byte vector accesses and 4-byte atomics.
+  if (workspace != nullptr && workspace_bytes > 0 && !aligned16(workspace)) {
+    return fail(LBL_ERR_INVALID, "workspace must be 16-byte aligned");
+  }
   if (Y == nullptr) return fail(LBL_ERR_INVALID, "Y is null");
   cudaStream_t cu_stream = static_cast<cudaStream_t>(stream);
 
@@ -199,7 +199,6 @@ int run_linear(const void* X, const int32_t* packed_w, const float* scales, cons
         if (workspace == nullptr || workspace_bytes < need) {
           return fail(LBL_ERR_WORKSPACE, "split-K needs %zu bytes of scratch, got %zu", need, workspace_bytes);
         }
-        if (!aligned16(workspace)) return fail(LBL_ERR_INVALID, "workspace must be 16-byte aligned");
         tickets = static_cast<int*>(workspace);
         partials = reinterpret_cast<float*>(static_cast<char*>(workspace) + plan.ticket_bytes);
       }
@@ -554,6 +553,9 @@ int lbl_w4a16_gemv_allreduce(const void* x, const int32_t* packed_w, const float
   for (int r = 0; r < world; ++r) {
     if (buffers[r] == nullptr) return fail(LBL_ERR_INVALID, "exchange buffer of rank %d is null", r);
   }
+  if (workspace != nullptr && workspace_bytes > 0 && !aligned16(workspace)) {
+    return fail(LBL_ERR_INVALID, "workspace must be 16-byte aligned");
+  }
   cudaStream_t cu_stream = static_cast<cudaStream_t>(stream);
   DeviceScope scope(device);
   if (!scope.ok()) return fail(LBL_ERR_CUDA, "cannot make device %d current", device);
@@ -590,6 +592,96 @@ int lbl_w4a16_gemv_allreduce(const void* x, const int32_t* packed_w, const float
   const cudaError_t err = lbl::launch_gemv_decode(prob, plan, partials, tickets, info.status_word,
                                                   (flags & LBL_FLAG_PDL) != 0, cu_stream, &reduce);
   if (err != cudaSuccess) return fail_cuda(err, "kernel launch");
+  return LBL_OK;
+}
+
+// ---------------------------------------------------------------------------------------------
+// Grouped decode GEMV: a list of independent problems in one persistent launch.
+// ---------------------------------------------------------------------------------------------
+struct lbl_w4a16_group {
+  lbl::GroupPlan* plan;
+};
+
+int lbl_w4a16_group_create(const lbl_w4a16_problem* problems, int count, int rank, int world,
+                           void* const* buffers, int64_t buffer_capacity_n, int device,
+                           lbl_w4a16_group** group) {
+  if (group == nullptr) return fail(LBL_ERR_INVALID, "group is null");
+  *group = nullptr;
+  if (problems == nullptr || count <= 0) return fail(LBL_ERR_INVALID, "a group needs at least one problem");
+  if (world < 1 || world > 8 || rank < 0 || rank >= world) return fail(LBL_ERR_INVALID, "bad rank/world");
+  lbl::PeerReduce exchange;
+  exchange.rank = rank;
+  exchange.world = world;
+  exchange.capacity_n = 0;
+  for (int r = 0; r < 8; ++r) exchange.buffers[r] = nullptr;
+  bool any_reduce = false;
+  std::vector<lbl::GroupProblemDesc> descs(static_cast<size_t>(count));
+  for (int i = 0; i < count; ++i) {
+    const lbl_w4a16_problem& q = problems[i];
+    if (q.x == nullptr || q.packed_w == nullptr || q.scales == nullptr || q.zeros == nullptr || q.y == nullptr) {
+      return fail(LBL_ERR_INVALID, "problem %d: null tensor pointer", i);
+    }
+    if (!aligned16(q.x) || !aligned16(q.packed_w) || !aligned16(q.scales) || !aligned16(q.zeros) || !aligned16(q.y)) {
+      return fail(LBL_ERR_INVALID, "problem %d: all tensors must be 16-byte aligned", i);
+    }
+    if (q.M < 1 || q.M > 2 || q.N < 1 || q.K < 256 || q.K % 256 != 0 || q.N > 0x7fffffffLL - 16 || q.M * q.K > 32768) {
+      return fail(LBL_ERR_UNSUPPORTED, "problem %d: the grouped GEMV serves 1 <= M <= 2, K %% 256 == 0, M * K <= 32768 (M=%lld N=%lld K=%lld)", i, (long long)q.M, (long long)q.N, (long long)q.K);
+    }
+    lbl::GroupProblemDesc& d = descs[static_cast<size_t>(i)];
+    d.x = q.x, d.packed = q.packed_w, d.scales = q.scales, d.zeros = q.zeros, d.y = q.y;
+    d.M = q.M, d.N = q.N, d.K = q.K;
+    d.reduce = q.reduce != 0 && world > 1;
+    any_reduce = any_reduce || d.reduce;
+  }
+  if (any_reduce) {
+    if (buffers == nullptr || buffer_capacity_n <= 0 || buffer_capacity_n % 4 != 0 || buffer_capacity_n > 0x7fffffffLL) {
+      return fail(LBL_ERR_INVALID, "problems with reduce=1 need the exchange buffers of all ranks");
+    }
+    for (int r = 0; r < world; ++r) {
+      if (buffers[r] == nullptr) return fail(LBL_ERR_INVALID, "exchange buffer of rank %d is null", r);
+      exchange.buffers[r] = buffers[r];
+    }
+    exchange.capacity_n = static_cast<int>(buffer_capacity_n);
+  }
+  DeviceScope scope(device);
+  if (!scope.ok()) return fail(LBL_ERR_CUDA, "cannot make device %d current", device);
+  DeviceInfo info;
+  const int rc = device_info(device, &info);
+  if (rc != LBL_OK) return rc;
+  lbl::GroupPlan* plan = nullptr;
+  const char* why = "";
+  const cudaError_t err = lbl::group_plan_create(descs.data(), count, info.sm_count, info.status_word,
+                                                 any_reduce ? &exchange : nullptr, &plan, &why);
+  if (err != cudaSuccess) {
+    if (why != nullptr && *why != '\0') return fail(LBL_ERR_UNSUPPORTED, "%s", why);
+    return fail_cuda(err, "group plan");
+  }
+  *group = new lbl_w4a16_group{plan};
+  return LBL_OK;
+}
+
+int lbl_w4a16_group_run(lbl_w4a16_group* group, unsigned flags, void* stream) {
+  if (group == nullptr || group->plan == nullptr) return fail(LBL_ERR_INVALID, "group is null");
+  DeviceScope scope(lbl::group_plan_device(group->plan));
+  if (!scope.ok()) return fail(LBL_ERR_CUDA, "cannot make the group's device current");
+  const cudaError_t err = lbl::launch_gemv_grouped(group->plan, (flags & LBL_FLAG_PDL) != 0,
+                                                   static_cast<cudaStream_t>(stream));
+  if (err != cudaSuccess) return fail_cuda(err, "kernel launch");
+  return LBL_OK;
+}
+
+int64_t lbl_w4a16_group_algorithmic_bytes(const lbl_w4a16_group* group) {
+  if (group == nullptr || group->plan == nullptr) return 0;
+  return lbl::group_plan_bytes(group->plan);
+}
+
+int lbl_w4a16_group_destroy(lbl_w4a16_group* group) {
+  if (group == nullptr) return LBL_OK;
+  if (group->plan != nullptr) {
+    DeviceScope scope(lbl::group_plan_device(group->plan));
+    lbl::group_plan_destroy(group->plan);
+  }
+  delete group;
   return LBL_OK;
 }
 

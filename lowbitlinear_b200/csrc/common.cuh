@@ -1,4 +1,4 @@
-// Shared device helpers for the sm_100a W4A16 kernels: mbarrier / bulk-copy / PDL wrappers with
+// Shared device helpers for the sm_100a W4A16 kernels: mbarrier / PDL wrappers with
 // bounded waits, the INT4 nibble extraction, and the legacy warp MMA used by the skinny kernel.
 #pragma once
 
@@ -98,17 +98,6 @@ __device__ __forceinline__ bool mbar_wait_bounded(uint64_t* bar, uint32_t parity
   }
 }
 
-// 1-D bulk copy global -> shared of `bytes` (multiple of 16, both addresses 16-byte aligned);
-// completion is signalled on `bar` as transaction bytes.  No multicast.
-__device__ __forceinline__ void bulk_load(void* smem_dst, const void* gmem_src, uint32_t bytes,
-                                          uint64_t* bar) {
-  asm volatile(
-      "cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::
-          "r"(smem_addr(smem_dst)),
-      "l"(gmem_src), "r"(bytes), "r"(smem_addr(bar))
-      : "memory");
-}
-
 // Programmatic dependent launch.  Both are no-ops when the launch did not ask for it.
 __device__ __forceinline__ void pdl_wait_for_previous_kernel() {
   asm volatile("griddepcontrol.wait;" ::: "memory");
@@ -144,7 +133,6 @@ __device__ __forceinline__ void mma_m16n8k16(float (&d)[4], const uint32_t (&a)[
 //   out[0] = (q0, q4)       out[1] = 16 * (q1, q5)
 //   out[2] = (q2, q6)       out[3] = 16 * (q3, q7)          (all times 2^-24)
 // ---------------------------------------------------------------------------------------------
-#ifndef LBL_BIASED_NIBBLES
 __device__ __forceinline__ void nibbles_as_subnormal_half2(uint32_t word, uint32_t (&out)[4]) {
   const uint32_t hi = word >> 8;
   out[0] = word & 0x000F000Fu;
@@ -153,22 +141,5 @@ __device__ __forceinline__ void nibbles_as_subnormal_half2(uint32_t word, uint32
   out[3] = hi & 0x00F000F0u;
 }
 constexpr float kNibbleUnit = 16777216.0f;  // 2^24: the MMA sees q * 2^-24
-#else
-// Build-time alternative that avoids subnormal operands: OR in the exponent of 1024 and
-// subtract 1024 again, which leaves q (or 16 q) as a normal FP16 number.  Four more
-// instructions per word.
-__device__ __forceinline__ void nibbles_as_subnormal_half2(uint32_t word, uint32_t (&out)[4]) {
-  const uint32_t hi = word >> 8;
-  const __half2 bias = __half2half2(__ushort_as_half(0x6400));
-  uint32_t v[4] = {(word & 0x000F000Fu) | 0x64006400u, (word & 0x00F000F0u) | 0x64006400u,
-                   (hi & 0x000F000Fu) | 0x64006400u, (hi & 0x00F000F0u) | 0x64006400u};
-#pragma unroll
-  for (int i = 0; i < 4; ++i) {
-    const __half2 r = __hsub2(*reinterpret_cast<const __half2*>(&v[i]), bias);
-    out[i] = *reinterpret_cast<const uint32_t*>(&r);
-  }
-}
-constexpr float kNibbleUnit = 1.0f;
-#endif
 
 }  // namespace lbl

@@ -279,15 +279,10 @@ __global__ void __launch_bounds__(kThreads, 2)
 // among 1..kMaxSlices (at least two super blocks of K per slice) take the smallest count whose
 // last wave is at least 90 % full, else the count with the fullest waves.
 int small_slices(int64_t N, int64_t K, int sm_count) {
-  const char* v = std::getenv("LBL_GEMM_SMALL_SLICES");
   const int64_t n_blocks = N / kRowsW;
   int64_t most = K / 256 / 2;
   if (most > kMaxSlices) most = kMaxSlices;
   if (most < 1) most = 1;
-  if (v != nullptr && *v != '\0') {
-    const int64_t forced = std::atoi(v);
-    return static_cast<int>(forced < 1 ? 1 : (forced > most ? most : forced));
-  }
   const int64_t wave = 2 * static_cast<int64_t>(sm_count > 0 ? sm_count : 148);
   int best = 1;
   double best_fill = 0.0;

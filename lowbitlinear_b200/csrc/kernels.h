@@ -78,6 +78,51 @@ cudaError_t launch_gemv_decode(const Problem& p, const SkinnyPlan& plan, float* 
 cudaError_t launch_skinny(const Problem& p, const SkinnyPlan& plan, float* partials, int* tickets,
                           int* status_word, bool pdl, cudaStream_t stream);
 
+// ----- all-reduce of FP32 vectors over peer memory (peer_reduce.cu) -----------------------------
+// Layout of an exchange buffer: a control block (CTAs done, epoch), one flag line per source
+// rank, then two FP32 vectors of capacity_n selected by the parity of the epoch.
+constexpr size_t kPeerDoneOffset = 0;
+constexpr size_t kPeerEpochOffset = 4;
+constexpr size_t kPeerFlagsOffset = 128;  // world flags, one 128-byte line each: flags[src] = epoch
+// One reduced output: `count` FP32 partial sums at `offset` floats into the vector -> dst FP16.
+struct ReduceSegment {
+  __half* dst;
+  int offset;
+  int count;
+};
+struct PeerReduceLaunch {
+  PeerReduce exchange;
+  const ReduceSegment* segments;  // device memory
+  int segment_count;
+  int longest;                    // largest count of any segment
+  int* status;
+};
+// Sums every segment over the ranks (in rank order, FP32) and writes FP16 to its dst on this GPU.
+// Every rank must launch it, after the kernel that wrote its own partial sums, on a stream of
+// its own device.  Advances the exchange's epoch.
+cudaError_t launch_peer_allreduce(const PeerReduceLaunch& launch, bool pdl, cudaStream_t stream);
+
+// ----- grouped decode GEMV (gemv_grouped.cu) ---------------------------------------------------
+struct GroupProblemDesc {
+  const void* x;
+  const int32_t* packed;
+  const float* scales;
+  const int32_t* zeros;
+  void* y;
+  int64_t M, N, K;
+  bool reduce;  // K-split shard: y receives the sum over the ranks of the exchange
+};
+struct GroupPlan;
+// Builds the plan (tensor maps, per-CTA work lists) in device memory of the current device.
+// Synchronous (cudaMalloc + cudaMemcpy).  `why` receives a reason when the shapes are refused.
+cudaError_t group_plan_create(const GroupProblemDesc* descs, int count, int sm_count, int* status_word,
+                              const PeerReduce* exchange, GroupPlan** out, const char** why);
+void group_plan_destroy(GroupPlan* plan);
+int group_plan_device(const GroupPlan* plan);
+int group_plan_count(const GroupPlan* plan);
+int64_t group_plan_bytes(const GroupPlan* plan);
+cudaError_t launch_gemv_grouped(const GroupPlan* plan, bool pdl, cudaStream_t stream);
+
 // ----- TMA + tcgen05 GEMM (gemm_tc.cu) ---------------------------------------------------------
 bool gemm_tc_supports(int64_t M, int64_t N, int64_t K);
 cudaError_t launch_gemm_tc(const Problem& p, int* status_word, cudaStream_t stream);

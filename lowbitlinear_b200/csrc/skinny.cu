@@ -5,11 +5,12 @@
 // slots per weight as possible.
 //
 // Data movement.  A persistent CTA walks a list of units; a unit is 16 weight rows by `kseg`
-// columns.  One producer warp streams the unit through a ring of shared-memory slots with 1-D
-// bulk copies (cp.async.bulk, completion counted on an mbarrier): per slot, 16 row pieces of
-// packed words plus the matching pieces of the scale and zero-point rows, each read straight
-// from the reference layout ([N, K/8] words, [N, K/64] metadata).  Row pieces land with a padded
-// pitch so that the fragment loads below are bank-conflict free.  Weight copies never depend on
+// columns.  One producer warp streams the unit through a ring of shared-memory slots with three
+// tiled TMA copies per slot (cp.async.bulk.tensor, completion counted on an mbarrier): 16 rows
+// of packed words plus the matching scale and zero-point rows, each read straight from the
+// reference layout ([N, K/8] words, [N, K/64] metadata).  The copy box is wider than the
+// tensor's inner extent, so the rows land with a zero-filled pad whose pitch keeps the fragment
+// loads below bank-conflict free at no cost in traffic.  Weight copies never depend on
 // the previous kernel in the stream, so with programmatic dependent launch they start while that
 // kernel is still draining; only the activation read waits for it.
 //
@@ -31,7 +32,6 @@
 #include "tensor_map.h"
 
 #include <algorithm>
-#include <cstdlib>
 #include <type_traits>
 
 namespace lbl {
@@ -392,12 +392,6 @@ __global__ void __launch_bounds__(kThreads, (NT <= 2 ? 2 : 1))
   }
 }
 
-int env_int(const char* name, int fallback) {
-  const char* v = std::getenv(name);
-  if (v == nullptr || *v == '\0') return fallback;
-  return std::atoi(v);
-}
-
 template <int NT>
 cudaError_t launch_nt(const CUtensorMap (&maps)[3], const KernelParams& kp, const SkinnyPlan& plan,
                       bool pdl, cudaStream_t stream) {
@@ -446,8 +440,7 @@ bool skinny_make_plan(int64_t M, int64_t N, int64_t K, int want_split, int sm_co
   // Candidate splits: every divisor d of K / 256 gives kseg = K / d.
   const int kseg_cap = std::max(256, (kXfBudgetBytes / (2 * m)) / 256 * 256);
   const int target_units = sm_count;  // split K only when the row tiles cannot fill the SMs
-  int forced = env_int("LBL_SKINNY_NSPLIT", 0);
-  if (want_split > 0) forced = want_split;
+  const int forced = want_split > 0 ? want_split : 0;
   int nsplit = 0;
   for (int d = 1; d <= chunks; ++d) {
     if (chunks % d != 0) continue;
@@ -467,8 +460,7 @@ bool skinny_make_plan(int64_t M, int64_t N, int64_t K, int want_split, int sm_co
   const int kseg = k / nsplit;
 
   int stage_k = 256;
-  const int stage_cap = std::min(kMaxStageK, std::max(256, env_int("LBL_SKINNY_STAGE_K", kMaxStageK)));
-  for (int c = stage_cap / 256; c >= 1; --c) {
+  for (int c = kMaxStageK / 256; c >= 1; --c) {
     if (kseg % (256 * c) == 0) {
       stage_k = 256 * c;
       break;
@@ -477,7 +469,7 @@ bool skinny_make_plan(int64_t M, int64_t N, int64_t K, int want_split, int sm_co
 
   // The decode form (M <= 2) reads 16 bytes per lane and needs a row pitch of 64 mod 128 bytes;
   // the general form reads 8 bytes per lane and needs 32 mod 128.
-  const bool columns = m <= 2 && env_int("LBL_GEMV_COLUMNS", 1) != 0;
+  const bool columns = m <= 2;
   const int packed_pad = columns ? 64 : 32;
   const int packed_pitch = stage_k / 2 + packed_pad;
   const int meta_pitch = stage_k / 16 + 16;
@@ -489,15 +481,14 @@ bool skinny_make_plan(int64_t M, int64_t N, int64_t K, int want_split, int sm_co
   const int xf_bytes = round128(m * kseg * 2);
   const int fixed = kHeaderBytes + sx_bytes + red_bytes + xf_bytes;
 
-  const int ctas_per_sm = std::max(1, std::min(2, env_int("LBL_SKINNY_CTAS_PER_SM", 2)));
-  int budget = ctas_per_sm == 2 ? env_int("LBL_SKINNY_SMEM_BUDGET", kSmemBudgetTwoCtas) : kSmemBudgetOneCta;
-  int per_sm = ctas_per_sm;
+  int budget = kSmemBudgetTwoCtas;
+  int per_sm = 2;
   if (fixed + 2 * slot_bytes > budget) {
     budget = kSmemBudgetOneCta;
     per_sm = 1;
   }
   int slots = (budget - fixed) / slot_bytes;
-  slots = std::min(slots, std::min(columns ? 6 : kMaxSlots, std::max(2, env_int("LBL_SKINNY_SLOTS", kMaxSlots))));
+  slots = std::min(slots, columns ? 6 : kMaxSlots);
   if (slots < 2) return false;
 
   const int64_t units = static_cast<int64_t>(row_tiles) * nsplit;

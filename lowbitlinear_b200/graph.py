@@ -1,10 +1,10 @@
-"""CUDA-graph runner for a sequence of quantised linears with static buffers.
+"""CUDA-graph runner for a set of quantised linears with static buffers.
 
 ``QuantizedLinear.forward`` re-validates its state and allocates its output on every call
 (as the reference does, ``lowbitlinear/linear.py:95-129``); at decode sizes that host work costs
-more than the kernels.  ``GraphedLinears`` validates once, captures the forward of every layer
-into one CUDA graph (``torch.cuda.CUDAGraph``: streams and graphs, no tracing compiler), and
-replays it on demand:
+more than the kernels.  ``GraphedLinears`` validates once, captures the work of every layer into
+one CUDA graph (``torch.cuda.CUDAGraph``: streams and graphs, no tracing compiler), and replays
+it on demand:
 
     runner = GraphedLinears(layers, m=1)            # layers: list of QuantizedLinear on one GPU
     runner.run(host_x, host_y)                      # pinned flat FP16 buffers in, out
@@ -12,7 +12,12 @@ replays it on demand:
 Each layer has its own activation ``[m, in_features]`` (views of one flat device buffer, in
 layer order) and writes its ``[m, out_features]`` result into a flat output buffer, so one
 host-to-device copy feeds a replay and one device-to-host copy returns everything.  The layers
-are independent here; a model runner would capture its own sequence the same way.
+are independent of each other.  For decode (``m <= 2``) the whole set is ONE persistent launch
+(``_ops.LinearGroup``); otherwise one launch per layer with programmatic dependent launch.
+
+Tensor parallel: give every rank its shards, flag the K-split (row-parallel) ones in ``reduce``
+and pass the ranks' ``PeerExchange``; the flagged outputs are summed over the ranks by the
+group's second kernel (decode) or by an NCCL all-reduce captured in the graph (larger ``m``).
 """
 import torch
 
@@ -22,7 +27,8 @@ from .linear import _validate_packed_weight
 
 
 class GraphedLinears:
-    def __init__(self, layers, m=1, programmatic_dependent_launch=True):
+    def __init__(self, layers, m=1, programmatic_dependent_launch=True, reduce=None, exchange=None,
+                 group=None, grouped=None):
         load_cuda_extension(required=True)
         layers = list(layers)
         if not layers:
@@ -36,6 +42,16 @@ class GraphedLinears:
         self.layers = layers
         self.m = m
         self.device = device
+        self.reduce = [False] * len(layers) if reduce is None else [bool(r) for r in reduce]
+        if len(self.reduce) != len(layers):
+            raise ValueError("reduce needs one entry per layer")
+        self.process_group = group
+        world = 1
+        if any(self.reduce):
+            import torch.distributed as dist
+
+            world = dist.get_world_size(group)
+        self.world = world
         # Offsets are multiples of 8 elements so that every view stays 16-byte aligned.
         pad = lambda v: (v + 7) // 8 * 8
         self.x_offsets, self.y_offsets = [], []
@@ -51,14 +67,36 @@ class GraphedLinears:
                    for o, l in zip(self.x_offsets, layers)]
         self.ys = [self.y_flat[o:o + m * l.out_features].view(m, l.out_features)
                    for o, l in zip(self.y_offsets, layers)]
+        can_group = m <= 2 and all(l.in_features % 256 == 0 and m * l.in_features <= 32768 for l in layers)
+        if grouped is None:
+            grouped = can_group
+        elif grouped and not can_group:
+            raise ValueError("the grouped launch needs m <= 2, in_features % 256 == 0 and m * in_features <= 32768")
+        self.grouped = grouped
+        self.linear_group = None
+        self.scratch = None
+        if grouped:
+            self.linear_group = _ops.LinearGroup(
+                [(x, l.packed_weight, l.scales, l.zeros, y, r and world > 1)
+                 for l, x, y, r in zip(layers, self.xs, self.ys, self.reduce)],
+                exchange=exchange if world > 1 else None)
+        else:
+            # The runner owns its split-K scratch: the captured graph holds the raw pointer, so the
+            # buffer must live exactly as long as the graph does.
+            need = max(_ops._lib.lbl_w4a16_workspace_bytes(m, l.out_features, l.in_features, _ops.PATH_AUTO)
+                       for l in layers)
+            self.scratch = torch.zeros(max(need, 16), dtype=torch.uint8, device=device)
         self.stream = torch.cuda.Stream(device=device)
         self.graph = torch.cuda.CUDAGraph()
         previous = _ops._flags
-        _ops.set_programmatic_dependent_launch(programmatic_dependent_launch)
+        # Between launches that alternate with NCCL kernels a dependent launch could hold SM
+        # resources a collective is waiting for, so it is used only without NCCL in the graph.
+        nccl_in_graph = world > 1 and not grouped
+        _ops.set_programmatic_dependent_launch(programmatic_dependent_launch and not nccl_in_graph)
         try:
             self.stream.wait_stream(torch.cuda.current_stream(device))
             with torch.cuda.stream(self.stream):
-                self._forward()  # warm-up: creates the per-stream scratch outside the capture
+                self._forward()  # warm-up outside the capture
             torch.cuda.current_stream(device).wait_stream(self.stream)
             torch.cuda.synchronize(device)
             with torch.cuda.graph(self.graph, stream=self.stream):
@@ -67,8 +105,15 @@ class GraphedLinears:
             _ops._flags = previous
 
     def _forward(self):
-        for layer, x, y in zip(self.layers, self.xs, self.ys):
-            _ops.linear_out(x, layer.packed_weight, layer.scales, layer.zeros, y)
+        if self.grouped:
+            self.linear_group.run()
+            return
+        for layer, x, y, reduce in zip(self.layers, self.xs, self.ys, self.reduce):
+            _ops.linear_out(x, layer.packed_weight, layer.scales, layer.zeros, y, workspace=self.scratch)
+            if reduce and self.world > 1:
+                import torch.distributed as dist
+
+                dist.all_reduce(y, group=self.process_group)
 
     def replay(self):
         """Replay on the current stream with whatever ``x_flat`` holds; results in ``y_flat``."""

@@ -65,6 +65,7 @@ class PeerExchange:
 
         lib = _extension.native()
         self._lib = lib
+        self.group = group
         self.rank, self.world = _world(group)
         self.capacity_n = int(max_n)
         self.device = torch.device(device)
@@ -95,14 +96,19 @@ class PeerExchange:
             raise RuntimeError(self._lib.lbl_last_error().decode())
 
     def close(self):
-        """Unmap the peers' buffers and free this rank's.  Call it on every rank, after the
-        last kernel that uses the exchange has finished."""
+        """Unmap the peers' buffers and free this rank's.  A collective call: every rank waits for
+        its own GPU and then for all the others before anything is unmapped, because a peer's last
+        kernel may still be reading this rank's vector when this rank's own kernel has finished.
+        Calling it again is a no-op."""
+        if self._own is None:
+            return
+        torch.cuda.synchronize(self.device)
+        dist.barrier(group=self.group)
         for mapped in self._opened:
             self._lib.lbl_peer_buffer_close(mapped, self.device.index)
         self._opened = []
-        if self._own is not None:
-            self._lib.lbl_peer_buffer_destroy(self._own, self.device.index)
-            self._own = None
+        self._lib.lbl_peer_buffer_destroy(self._own, self.device.index)
+        self._own = None
 
 
 class ColumnParallelLinear(torch.nn.Module):

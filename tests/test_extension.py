@@ -1,6 +1,8 @@
 """The drop-in boundary: the native library loads, exports every entry point the header
 declares, registers the reference's two operator schemas, and a missing library is an error
-for CUDA work but not for CPU work.  No GPU compute happens in the CPU-marked tests."""
+for CUDA work but not for CPU work.  No GPU compute happens in the CPU-marked tests.
+The fresh-process schema test and the shape and error tables are adapted from NanjinLin/LowBitLinear
+tests/test_api_dispatch.py (MIT)."""
 import ctypes
 import os
 import re
@@ -64,12 +66,63 @@ def test_argument_errors_need_no_gpu():
 
 
 @needs_library
+def test_misaligned_workspace_is_rejected_before_anything_is_launched():
+    """A sub-allocated scratch pointer that is not 16-byte aligned would fault on the device (vector
+    loads, atomics); the C ABI refuses it on the host, for every entry point that takes one."""
+    lib = ctypes.CDLL(str(LIBRARY))
+    lib.lbl_last_error.restype = ctypes.c_char_p
+    p, i64, i32, u32, sz = ctypes.c_void_p, ctypes.c_int64, ctypes.c_int, ctypes.c_uint, ctypes.c_size_t
+    lib.lbl_w4a16_gemm.argtypes = [p, p, p, p, p, i64, i64, i64, p, sz, u32, i32, p]
+    rc = lib.lbl_w4a16_gemm(16, 16, 16, 16, 16, 16, 256, 512, 1024 + 8, 1 << 20, 0, 0, None)
+    assert rc == -1 and b"workspace must be 16-byte aligned" in lib.lbl_last_error()
+    lib.lbl_w4a16_linear.argtypes = [p, p, p, p, p, i64, i64, i64, i32, i32, p, sz, u32, i32, p, p]
+    rc = lib.lbl_w4a16_linear(16, 16, 16, 16, 16, 16, 256, 512, 1, 5, 1024 + 4, 1 << 20, 0, 0, None, None)
+    assert rc == -1 and b"workspace must be 16-byte aligned" in lib.lbl_last_error()
+    lib.lbl_w4a16_gemv.argtypes = [p, p, p, p, p, i64, i64, i32, p, sz, u32, i32, p]
+    rc = lib.lbl_w4a16_gemv(16, 16, 16, 16, 16, 256, 4096, 64, 1024 + 2, 1 << 20, 0, 0, None)
+    assert rc == -1 and b"workspace must be 16-byte aligned" in lib.lbl_last_error()
+    lib.lbl_w4a16_gemv_allreduce.argtypes = [p, p, p, p, p, i64, i64, i32, i32, i32, ctypes.POINTER(p), i64,
+                                             p, sz, u32, i32, p]
+    buffers = (p * 2)(4096, 8192)
+    rc = lib.lbl_w4a16_gemv_allreduce(16, 16, 16, 16, 16, 256, 4096, 64, 0, 2, buffers, 256, 1024 + 8, 1 << 20,
+                                      0, 0, None)
+    assert rc == -1 and b"workspace must be 16-byte aligned" in lib.lbl_last_error()
+
+
+@needs_library
+def test_group_argument_errors_need_no_gpu():
+    from lowbitlinear_b200 import _ops
+
+    lib = ctypes.CDLL(str(LIBRARY))
+    lib.lbl_last_error.restype = ctypes.c_char_p
+    p = ctypes.c_void_p
+    lib.lbl_w4a16_group_create.argtypes = [ctypes.POINTER(_ops.GroupProblem), ctypes.c_int, ctypes.c_int, ctypes.c_int,
+                                           ctypes.POINTER(p), ctypes.c_int64, ctypes.c_int, ctypes.POINTER(p)]
+    handle = p()
+    problems = (_ops.GroupProblem * 1)()
+    assert lib.lbl_w4a16_group_create(problems, 0, 0, 1, None, 0, 0, ctypes.byref(handle)) == -1
+    assert lib.lbl_w4a16_group_create(problems, 1, 0, 1, None, 0, 0, ctypes.byref(handle)) == -1
+    assert b"null tensor pointer" in lib.lbl_last_error()
+    q = problems[0]
+    q.x = q.packed_w = q.scales = q.zeros = q.y = 4096
+    q.M, q.N, q.K = 3, 64, 256
+    assert lib.lbl_w4a16_group_create(problems, 1, 0, 1, None, 0, 0, ctypes.byref(handle)) == -4
+    assert b"grouped GEMV serves" in lib.lbl_last_error()
+    q.M, q.reduce = 1, 1
+    assert lib.lbl_w4a16_group_create(problems, 1, 0, 2, None, 0, 0, ctypes.byref(handle)) == -1
+    assert b"exchange buffers" in lib.lbl_last_error()
+    q.y = 4096 + 8
+    assert lib.lbl_w4a16_group_create(problems, 1, 0, 1, None, 0, 0, ctypes.byref(handle)) == -1
+    assert b"16-byte aligned" in lib.lbl_last_error() and handle.value is None
+
+
+@needs_library
 def test_dispatcher_choices_and_scratch_sizes():
     from lowbitlinear_b200 import _ops
     from lowbitlinear_b200._extension import load_cuda_extension
 
     assert load_cuda_extension(required=True)
-    env_backup = {k: os.environ.pop(k, None) for k in ("LBL_FORCE_PATH", "LBL_SKINNY_NSPLIT", "LBL_TC_MIN_M")}
+    env_backup = {k: os.environ.pop(k, None) for k in ("LBL_FORCE_PATH",)}
     try:
         name = lambda m, n, k: _ops.PATH_NAMES[_ops.select_path(m, n, k)]
         # Decode shapes stream; a small N or a long K is split across CTAs.

@@ -1,5 +1,7 @@
 """Public module on CPU: reference path against the oracle and the reference's fixtures, state
-handling, validation.  Mirrors the intent of the reference's tests/test_linear.py."""
+handling, validation.  Adapted from NanjinLin/LowBitLinear tests/test_linear.py (MIT): the constructor, forward-error and
+device cases follow that file closely (its parametrisations pin the API contract); the oracle,
+the golden fixtures and the no-library CPU test are this repository's."""
 import numpy as np
 import pytest
 import torch

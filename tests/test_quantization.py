@@ -1,6 +1,8 @@
 """The package's torch quantiser / packer: bit-exact against the oracle and the reference's
-fixtures, partial groups and words, error contract.  Mirrors the intent of the reference's
-tests/test_quantization.py."""
+fixtures, partial groups and words, error contract.  Adapted from NanjinLin/LowBitLinear
+tests/test_quantization.py (MIT): its known-answer vectors and validation-error table are kept
+because they define the format; the main quantiser test is rewritten around the oracle and the
+golden fixtures."""
 import numpy as np
 import pytest
 import torch

@@ -30,12 +30,12 @@ def _bind():
     return lib
 
 
-def _call_noalloc(lib, x, packed, scales, zeros):
+def _call_noalloc(lib, x, packed, scales, zeros, flags=0):
     n, k = packed.shape[0], x.shape[1]
     y = torch.empty((1, n), dtype=torch.float16, device=x.device)  # outputs belong to the caller
     stream = torch.cuda.current_stream(x.device).cuda_stream
     rc = lib.lbl_w4a16_gemv_noalloc(x.data_ptr(), packed.data_ptr(), scales.data_ptr(), zeros.data_ptr(),
-                                    y.data_ptr(), n, k, 64, 0, x.device.index, stream)
+                                    y.data_ptr(), n, k, 64, flags, x.device.index, stream)
     assert rc == 0, lib.lbl_last_error().decode()
     return y
 
@@ -57,6 +57,23 @@ def test_noalloc_gemv_matches_the_regular_entry_point_twice(n, k, cuda_ops):
     torch.testing.assert_close(first.cpu(), oracle_linear(x, packed, scales, zeros), atol=ATOL, rtol=RTOL)
     # Same inputs again give the same bits: the counters were left at zero.
     assert torch.equal(_call_noalloc(lib, x, packed, scales, zeros), first)
+
+
+def test_noalloc_gemv_chain_with_programmatic_dependent_launch(cuda_ops):
+    """With LBL_FLAG_PDL consecutive calls overlap in time on the GPU: a call starts fetching its
+    weights while the previous one is still finishing, yet both use the one built-in scratch.
+    What keeps that correct is that no call touches the scratch before the previous kernel has
+    completed.  Eight calls back to back, two shapes alternating, no host synchronisation in
+    between, three rounds; every output must equal that of the same call made alone."""
+    lib = _bind()
+    cases = [seeded_layer(1, 4096, 4096, seed=71, device=cuda_ops), seeded_layer(1, 1000, 2048, seed=72, device=cuda_ops)]
+    alone = [_call_noalloc(lib, *case) for case in cases]
+    torch.cuda.synchronize()
+    for _ in range(3):
+        chained = [_call_noalloc(lib, *cases[i % 2], flags=1) for i in range(8)]
+        torch.cuda.synchronize()
+        for i, y in enumerate(chained):
+            assert torch.equal(y, alone[i % 2]), i
 
 
 def test_noalloc_gemv_rejects_what_does_not_fit(cuda_ops):
