@@ -1,27 +1,37 @@
 #!/usr/bin/env python
 """Benchmark of the W4A16 linear forward at Qwen3-8B linear shapes on B200.
 
-    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference]
-                    [--workload decode|prefill] [--pdl 0|1]
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference|reference_gpu]
+                    [--workload stack|decode|prefill|crossover|prefill_sweep]
 
 Workload (synthetic, random-init, no checkpoint): the 36 decoder layers of a Qwen3-8B-shaped
 model, four linears per layer -- QKV 6144x4096, O 4096x4096, Gate/Up 24576x4096,
 Down 4096x12288 -- with group-64 asymmetric INT4 weights from N(0, 0.02) and FP16 activations
 from N(0, 1).  One step is one pass over all 144 linears, each with its own activation:
 
-  decode  (default)  M = 1.     Metric: achieved HBM GB/s = algorithmic bytes / time, where the
-                                bytes of one linear are N K / 2 + 8 N K / 64 + 2 M K + 2 M N.
-  prefill            M = 2048.  Metric: achieved TFLOP/s = 2 M N K / time.
+  decode   M = 1.     Metric: achieved HBM GB/s = algorithmic bytes / time, where the bytes of one
+                      linear are N K / 2 + 8 N K / 64 + 2 M K + 2 M N.  The 144 independent
+                      linears run as ONE grouped launch (lbl_w4a16_group_run).
+  prefill  M = 2048.  Metric: achieved TFLOP/s = 2 M N K / time, one launch per linear.
+  stack    (default)  both: the JSON line's `value` is the decode figure, its `gemm` block the
+                      prefill figure.
+  crossover      benchmark config 3: the four shapes at M in {2..64}, every kernel path forced
+                 plus the dispatcher's pick, weights rotating through more than the L2.
+  prefill_sweep  benchmark config 4: Gate/Up and Down at M in {128, 512, 2048, 8192}.
 
 The 144 weight sets total 4.3 GB, far more than the 126 MB L2, so every step streams from HBM.
-The device-timed value replays a CUDA graph of the 144 launches (inputs resident in HBM); the
-`e2e` value goes through the public Python API (QuantizedLinear.forward) from pinned host
+Device-timed values replay a CUDA graph of the step (inputs resident in HBM), each step between
+its own pair of CUDA events; `e2e` goes through the package's public runner from pinned host
 activations to host outputs, copies included.  With N > 1 (torchrun) the stack is tensor
-parallel: QKV, O and Gate/Up are split along N, Down along K with an NCCL all-reduce; the
-total work is fixed (strong scaling) and the time is the maximum over ranks.
+parallel: QKV, O and Gate/Up are split along N, Down along K with an all-reduce over NVLink (peer
+memory kernel for decode, NCCL for prefill); total work is fixed (strong scaling), time is the
+maximum over ranks, and every rank's layer-0 outputs are checked against the CPU reference.
 
-`--impl reference` times the reference algorithm's CPU path (the numpy oracle under oracle/,
-a restatement of lowbitlinear/linear.py:43-70 of NanjinLin/LowBitLinear) on the host cores.
+`--impl reference` times the reference's own CPU path, `linear_int4_reference` of
+NanjinLin/LowBitLinear (lowbitlinear/linear.py:43-70), imported from oracle/_ref when that
+install exists (oracle/make_ref.py) and restated by the numpy oracle otherwise.
+`--impl reference_gpu` (crossover / prefill_sweep only) times the reference's own CUDA operators,
+compiled for sm_100a by the same install, in a process that never loads this library.
 """
 import argparse
 import json
@@ -29,6 +39,7 @@ import os
 import statistics
 import subprocess
 import sys
+import tempfile
 import threading
 import time
 from pathlib import Path
@@ -42,6 +53,9 @@ sys.path.insert(0, str(ROOT))
 SHAPES = [("qkv", 6144, 4096), ("o", 4096, 4096), ("gate_up", 24576, 4096), ("down", 4096, 12288)]
 LAYERS = 36
 WEIGHT_STD = 0.02
+PREFILL_M = 2048
+REF_DIR = ROOT / "oracle" / "_ref"
+TOLERANCE = "rel L2 <= 1e-3, |a-b| <= 1e-2 + 1e-2|b|"
 
 
 def linear_bytes(m, n, k):
@@ -61,62 +75,90 @@ def measured_peaks():
     return {"hbm_gbs": 6650.0, "tflops_burst": 1590.0, "tflops_sustained": 1400.0, "source": "fallback"}
 
 
+def traffic_ratio(kernel):
+    """DRAM bytes (read + write) per algorithmic byte of one launch of `kernel`, from the ncu
+    capture summarised under profiles/ (profiles/traffic.json); None when there is no capture."""
+    path = ROOT / "profiles" / "traffic.json"
+    if not path.is_file():
+        return None, None
+    entry = json.loads(path.read_text()).get(kernel)
+    if not entry:
+        return None, None
+    return entry.get("dram_bytes_per_algorithmic_byte"), entry.get("source")
+
+
+def summary(samples_ms):
+    """Median / P90 / min / max of per-step times, as the reference's harness reports them
+    (benchmarks/_common.py:175-181)."""
+    ordered = sorted(samples_ms)
+    p90 = ordered[min(len(ordered) - 1, int(round(0.9 * (len(ordered) - 1))))]
+    return {"median_ms": statistics.median(ordered), "p90_ms": p90, "min_ms": ordered[0], "max_ms": ordered[-1],
+            "samples": len(ordered)}
+
+
 # ------------------------------------------------------------------------------------------------
-# Clock sampling during the timed region
+# Clock sampling during the timed region (read-only NVML queries from a thread)
 # ------------------------------------------------------------------------------------------------
 class ClockSampler:
-    FIELDS = ("clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.hw_slowdown,"
-              "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
-              "clocks_event_reasons.sw_power_cap")
+    REASONS = {"hw_slowdown": 0x8, "sw_power_cap": 0x4, "hw_thermal_slowdown": 0x40, "sw_thermal_slowdown": 0x20}
 
-    def __init__(self, device_index):
+    def __init__(self, device_index, period_s=0.002):
         self.rows = []
-        self.proc = None
+        self.period = period_s
+        self.stop_flag = False
+        self.handle = None
+        self.thread = None
         try:
+            import pynvml
+            pynvml.nvmlInit()
             uuid = str(torch.cuda.get_device_properties(device_index).uuid)
             if not uuid.startswith("GPU-"):
                 uuid = "GPU-" + uuid
-            self.proc = subprocess.Popen(
-                ["nvidia-smi", "-i", uuid, f"--query-gpu={self.FIELDS}", "--format=csv,noheader,nounits",
-                 "-lms", "100"], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
-            self.thread = threading.Thread(target=self._read, daemon=True)
+            self.nvml = pynvml
+            self.handle = pynvml.nvmlDeviceGetHandleByUUID(uuid.encode())
+            self.max_sm = pynvml.nvmlDeviceGetMaxClockInfo(self.handle, pynvml.NVML_CLOCK_SM)
+            self.thread = threading.Thread(target=self._loop, daemon=True)
             self.thread.start()
-        except (OSError, RuntimeError, AttributeError):
-            self.proc = None
+        except Exception:  # noqa: BLE001  (no NVML: the line says so)
+            self.handle = None
 
-    def _read(self):
-        for line in self.proc.stdout:
-            self.rows.append((time.perf_counter(), line.strip()))
-
-    def stop(self, t0, t1):
-        if self.proc is None:
-            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
-        time.sleep(0.15)
-        self.proc.terminate()
-        try:
-            self.proc.wait(timeout=5)
-        except subprocess.TimeoutExpired:
-            self.proc.kill()
-        inside = [r for t, r in self.rows if t0 <= t <= t1 + 0.1] or [r for _, r in self.rows[-3:]]
-        sm, sm_max, power, reasons = [], [], [], set()
-        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
-        for row in inside:
-            parts = [p.strip() for p in row.split(",")]
-            if len(parts) < 7:
-                continue
+    def _loop(self):
+        nv = self.nvml
+        while not self.stop_flag:
             try:
-                sm.append(float(parts[0]))
-                sm_max.append(float(parts[1]))
-                power.append(float(parts[2]))
-            except ValueError:
-                continue
-            for name, flag in zip(names, parts[3:7]):
-                if flag.lower().startswith("active"):
+                sm = nv.nvmlDeviceGetClockInfo(self.handle, nv.NVML_CLOCK_SM)
+                reasons = nv.nvmlDeviceGetCurrentClocksEventReasons(self.handle)
+                power = nv.nvmlDeviceGetPowerUsage(self.handle) / 1000.0
+                self.rows.append((time.perf_counter(), sm, reasons, power))
+            except Exception:  # noqa: BLE001
+                pass
+            time.sleep(self.period)
+
+    def window(self, t0, t1):
+        """Clock record of [t0, t1]; when the region was too short for three samples, the
+        samples of the warm-up right before it (same load) are included and that is stated."""
+        if self.handle is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["NVML unavailable"]}
+        inside = [r for r in self.rows if t0 <= r[0] <= t1]
+        note = "sampled inside the timed region"
+        if len(inside) < 3:
+            inside = [r for r in self.rows if t0 - 0.25 <= r[0] <= t1 + 0.005]
+            note = "timed region shorter than three samples: includes the warm-up replays just before it"
+        if not inside:
+            return {"sm_mhz": None, "sm_max_mhz": float(self.max_sm), "reasons": ["no samples"], "samples": 0}
+        reasons = set()
+        for _, _, mask, _ in inside:
+            for name, bit in self.REASONS.items():
+                if mask & bit:
                     reasons.add(name)
-        return {"sm_mhz": statistics.median(sm) if sm else None,
-                "sm_max_mhz": max(sm_max) if sm_max else None,
-                "power_w": statistics.median(power) if power else None,
-                "samples": len(sm), "reasons": sorted(reasons)}
+        return {"sm_mhz": statistics.median(r[1] for r in inside), "sm_max_mhz": float(self.max_sm),
+                "power_w": statistics.median(r[3] for r in inside), "samples": len(inside),
+                "reasons": sorted(reasons), "window": note}
+
+    def close(self):
+        self.stop_flag = True
+        if self.thread is not None:
+            self.thread.join(timeout=1.0)
 
 
 # ------------------------------------------------------------------------------------------------
@@ -139,86 +181,120 @@ def shard_dims(name, n, k, world):
     return n // world, k
 
 
-def build_stack(m, device, rank, world, host_layer0):
-    """Quantised layers and activations resident on `device`.  Layer 0 comes from the seeded CPU
-    tensors in `host_layer0` (so that CPU baseline and GPU see identical bits, at world 1);
-    the other layers are drawn and quantised on the GPU from per-linear seeds."""
+def shard_of(name, tensor_nk, rank, world, per_k):
+    """Rank's slice of a [N, K / per_k] buffer of a full linear (rows, or columns for Down)."""
+    if world == 1:
+        return tensor_nk
+    if name == "down":
+        cols = tensor_nk.shape[1] // world
+        return tensor_nk[:, rank * cols:(rank + 1) * cols].contiguous()
+    rows = tensor_nk.shape[0] // world
+    return tensor_nk[rank * rows:(rank + 1) * rows].contiguous()
+
+
+def build_layers(device, rank, world, host_layer0):
+    """Quantised (sharded) layers resident on `device`.  Layer 0 is cut from the seeded CPU tensors
+    in `host_layer0` (packed, scales, zeros per linear), so that the CPU reference and every rank
+    see identical bits; the other layers are drawn and quantised on the GPU from per-linear seeds."""
     from lowbitlinear_b200 import QuantizedLinear
 
-    layers, xs = [], []
+    layers = []
     for layer in range(LAYERS):
         for idx, (name, n, k) in enumerate(SHAPES):
             ns, ks = shard_dims(name, n, k, world)
-            if layer == 0 and world == 1 and host_layer0 is not None:
-                x, packed, scales, zeros = host_layer0[idx]
-                q_layer = QuantizedLinear(packed.to(device), scales.to(device), zeros.to(device), in_features=k)
-                x = x.to(device)
+            if layer == 0 and host_layer0 is not None:
+                packed, scales, zeros = host_layer0[idx]
+                q_layer = QuantizedLinear(shard_of(name, packed, rank, world, 8).to(device),
+                                          shard_of(name, scales, rank, world, 64).to(device),
+                                          shard_of(name, zeros, rank, world, 64).to(device), in_features=ks)
             else:
                 g = torch.Generator(device=device).manual_seed(100003 * rank + 1000 * layer + idx)
                 weight = (torch.randn(ns, ks, device=device, generator=g) * WEIGHT_STD).half()
-                x = torch.randn(m, ks, device=device, generator=g).half()
                 q_layer = QuantizedLinear.from_float(weight)
                 del weight
             layers.append((name, q_layer))
-            xs.append(x)
-    return layers, xs
+    return layers
 
 
-EXCHANGE = None  # PeerExchange of a tensor-parallel decode run: all-reduce fused into the GEMV
-
-
-def run_stack(layers, xs, world):
-    """One pass over the stack through the public operators; returns the outputs.  Between
-    tensor-parallel ranks the K-split Down projection ends in an all-reduce: fused into the
-    decode kernel over peer memory when an exchange is set up, NCCL otherwise."""
-    import torch.distributed as dist
-
-    from lowbitlinear_b200 import _ops
-
-    outs = []
-    for (name, layer), x in zip(layers, xs):
-        if world > 1 and name == "down":
-            if EXCHANGE is not None and x.shape[0] == 1:
-                y = _ops.gemv_allreduce(x, layer.packed_weight, layer.scales, layer.zeros, EXCHANGE)
-            else:
-                y = layer(x)
-                dist.all_reduce(y)
+def fill_activations(runner, layers, m, device, rank, world, host_x0):
+    """Seeded activations into the runner's static buffer; layer 0 gets the CPU reference's x."""
+    for i, ((name, layer), x_view) in enumerate(zip(layers, runner.xs)):
+        if i < len(SHAPES) and host_x0 is not None:
+            x = host_x0[i]
+            if world > 1 and name == "down":
+                part = layer.in_features
+                x = x[:, rank * part:(rank + 1) * part]
+            x_view.copy_(x.to(device))
         else:
-            y = layer(x)
-        outs.append(y)
-    return outs
+            g = torch.Generator(device=device).manual_seed(7 + 100003 * rank + i + 1009 * m)
+            x_view.copy_(torch.randn(m, layer.in_features, device=device, generator=g).half())
 
 
 # ------------------------------------------------------------------------------------------------
-# CPU baseline (oracle) -- checker and reported baseline, never the product path
+# Reference arm: the reference's own CPU path on the host cores (own process, never this library)
 # ------------------------------------------------------------------------------------------------
-def oracle_sample(m, shape_indices, repeats=1):
-    """Times the numpy oracle on the given linears of layer 0; returns (seconds per pass,
-    per-linear inputs and oracle outputs as torch CPU tensors)."""
+def reference_functions():
+    """(linear_int4_reference, quantize, kind): from the reference install when present."""
+    if (REF_DIR / "lowbitlinear" / "linear.py").is_file():
+        sys.path.insert(0, str(REF_DIR))
+        from lowbitlinear.linear import linear_int4_reference
+        from lowbitlinear.quantization import pack_int4, quantize_int4
+
+        def quantize(weight):
+            q, scales, zeros = quantize_int4(weight, 64)
+            return pack_int4(q), scales, zeros
+
+        return linear_int4_reference, quantize, "reference"
     from oracle import w4a16_oracle as oracle
 
+    def quantize(weight):
+        q, scales, zeros = oracle.quantize_int4(weight.numpy(), 64)
+        return torch.from_numpy(oracle.pack_int4(q)), torch.from_numpy(scales), torch.from_numpy(zeros)
+
+    def linear(x, packed, scales, zeros, group_size=64):
+        return torch.from_numpy(oracle.linear_int4_reference(x.numpy(), packed.numpy(), scales.numpy(), zeros.numpy()))
+
+    return linear, quantize, "port"
+
+
+def cpu_description(kind):
+    model = ""
+    try:
+        for line in Path("/proc/cpuinfo").read_text().splitlines():
+            if line.startswith("model name"):
+                model = line.split(":", 1)[1].strip()
+                break
+    except OSError:
+        pass
+    return {"kind": kind, "cores": torch.get_num_threads(), "cpu_count": os.cpu_count(), "cpu_model": model,
+            "implementation": ("lowbitlinear.linear.linear_int4_reference of the unmodified reference (oracle/_ref)"
+                               if kind == "reference" else "numpy restatement (oracle/w4a16_oracle.py); oracle/_ref absent")}
+
+
+def reference_sample(m, shape_indices, passes, warmup, emit=None):
+    """Times `passes` evaluations of the given layer-0 linears on the host cores.  Returns
+    (seconds per pass, per-pass list, kind); with `emit` also saves inputs and outputs."""
+    linear, quantize, kind = reference_functions()
     prepared = []
     for idx in shape_indices:
         x, weight = cpu_layer_inputs(m, idx)
-        q, scales, zeros = oracle.quantize_int4(weight.numpy(), 64)
-        prepared.append((idx, x.numpy(), oracle.pack_int4(q), scales, zeros))
-    times, outputs = [], None
-    for _ in range(repeats):
-        t0 = time.perf_counter()
-        outputs = [oracle.linear_int4_reference(x, p, s, z) for _, x, p, s, z in prepared]
-        times.append(time.perf_counter() - t0)
-    tensors = {idx: (torch.from_numpy(x), torch.from_numpy(p), torch.from_numpy(s), torch.from_numpy(z))
-               for idx, x, p, s, z in prepared}
-    return statistics.median(times), tensors, {idx: torch.from_numpy(y) for (idx, *_), y in zip(prepared, outputs)}
-
-
-def blas_threads():
-    try:
-        from threadpoolctl import threadpool_info
-        counts = [info.get("num_threads", 1) for info in threadpool_info()]
-        return max(counts) if counts else os.cpu_count()
-    except Exception:  # noqa: BLE001
-        return os.cpu_count()
+        packed, scales, zeros = quantize(weight)
+        prepared.append((idx, x, packed, scales, zeros))
+    outputs = None
+    times = []
+    with torch.inference_mode():
+        for it in range(warmup + passes):
+            t0 = time.perf_counter()
+            outputs = [linear(x, p, s, z, 64) for _, x, p, s, z in prepared]
+            if it >= warmup:
+                times.append(time.perf_counter() - t0)
+    if emit is not None:
+        arrays = {}
+        for (idx, x, p, s, z), y in zip(prepared, outputs):
+            arrays.update({f"x{idx}": x.numpy(), f"packed{idx}": p.numpy(), f"scales{idx}": s.numpy(),
+                           f"zeros{idx}": z.numpy(), f"y{idx}": y.numpy()})
+        np.savez(emit, **arrays)
+    return sum(times) / len(times), times, kind
 
 
 def unit_and_amount(workload, m, shape_indices):
@@ -228,61 +304,79 @@ def unit_and_amount(workload, m, shape_indices):
 
 
 def metric_name(workload):
+    decode = "W4A16 decode GEMV achieved HBM GB/s, Qwen3-8B linear shapes (36-layer stack, M=1)"
+    prefill = f"W4A16 prefill GEMM achieved TFLOP/s, Qwen3-8B linear shapes (36-layer stack, M={PREFILL_M})"
     if workload == "decode":
-        return "W4A16 decode GEMV achieved HBM GB/s, Qwen3-8B linear shapes (36-layer stack, M=1)"
-    return "W4A16 prefill GEMM achieved TFLOP/s, Qwen3-8B linear shapes (36-layer stack, M=2048)"
+        return decode
+    if workload == "prefill":
+        return prefill
+    return decode + "; `gemm` block: " + prefill
 
 
-def config_of(workload, m, world, pdl):
-    return {"workload": f"qwen3_8b_linear_stack_{workload}_m{m}",
+def config_of(workload, world):
+    """Identical for both arms of a run (the reference arm measures a bounded sample of it)."""
+    return {"workload": {"stack": f"qwen3_8b_linear_stack_decode_m1+prefill_m{PREFILL_M}",
+                         "decode": "qwen3_8b_linear_stack_decode_m1",
+                         "prefill": f"qwen3_8b_linear_stack_prefill_m{PREFILL_M}"}[workload],
             "layers": LAYERS, "linears_per_layer": [f"{n}:{N}x{K}" for n, N, K in SHAPES],
-            "M": m, "group_size": 64, "weights": "int4 asymmetric, N(0,0.02)", "activations": "fp16 N(0,1)",
+            "M": {"stack": [1, PREFILL_M], "decode": [1], "prefill": [PREFILL_M]}[workload], "group_size": 64,
+            "weights": "int4 asymmetric, N(0,0.02)", "activations": "fp16 N(0,1)",
             "parallelism": f"tp{world}" if world > 1 else "single",
-            "l2": "inputs (4.3 GB of weights per step) are larger than the 126 MB L2",
-            "launch": "CUDA graph replay of 144 linears per step", "pdl": bool(pdl)}
+            "l2": "inputs (4.3 GB of weights per step) are larger than the 126 MB L2"}
 
 
-# ------------------------------------------------------------------------------------------------
-# Reference arm: the reference algorithm's CPU path on the host cores
-# ------------------------------------------------------------------------------------------------
 def run_reference_arm(args):
     rank = int(os.environ.get("RANK", "0"))
     if rank != 0:
         return
-    m = 1 if args.workload == "decode" else 2048
-    budget_s = 150.0
-    # Pick a sample that keeps (warmup + steps) passes inside the budget.
-    t_o, _, _ = oracle_sample(m, [1])
-    passes = args.warmup + args.steps
-    indices = [0, 1, 2, 3] if passes * t_o * 12.0 <= budget_s else [1]
-    for _ in range(args.warmup):
-        oracle_sample(m, indices)
-    times = []
-    for _ in range(args.steps):
-        t, _, _ = oracle_sample(m, indices)
-        times.append(t)
-    per_step = sum(times) / len(times)
-    unit, amount = unit_and_amount(args.workload, m, indices)
-    value = amount / per_step
-    sample = ("one layer (QKV, O, Gate/Up, Down)" if len(indices) == 4 else "the O projection 4096x4096") + f" at M={m} per step"
-    cores = blas_threads()
-    line = {"impl": "reference", "metric": metric_name(args.workload), "value": value, "unit": unit,
-            "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup, "ms_per_step": per_step * 1e3,
-            "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "f32",
-            "data": "synthetic", "config": config_of(args.workload, m, 1, 0),
-            "cpu_baseline": {"value": value, "unit": unit, "cores": cores, "kind": "port", "sample": sample},
-            "e2e": {"value": value, "unit": unit, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
-            "gpu_launches": 0}
+    # All the host threads there are (torchrun sets OMP_NUM_THREADS=1 for its workers).
+    torch.set_num_threads(max(1, os.cpu_count() or 1))
+    if args.emit:  # helper mode of our own arm: layer 0 at M = 1, inputs and outputs saved
+        seconds, times, kind = reference_sample(1, [0, 1, 2, 3], passes=max(1, args.steps), warmup=min(1, args.warmup),
+                                                emit=args.emit)
+        print(json.dumps({"seconds_per_pass": seconds, "times": times, **cpu_description(kind)}), flush=True)
+        return
+    workload = args.workload if args.workload in ("decode", "prefill", "stack") else "stack"
+    passes = max(1, args.steps)
+    line = {"impl": "reference", "metric": metric_name(workload), "n_gpus": args.gpus, "steps": args.steps,
+            "warmup": args.warmup, "higher_is_better": True, "scaling": "strong", "vs_baseline": None,
+            "dtype": "f32", "data": "synthetic", "config": config_of(workload, args.gpus), "gpu_launches": 0}
+    blocks = {}
+    for part in (["decode", "prefill"] if workload == "stack" else [workload]):
+        m = 1 if part == "decode" else PREFILL_M
+        # Bounded sample: one layer at M = 1 (about a second per pass); the O projection at M = 2048.
+        indices = [0, 1, 2, 3] if part == "decode" else [1]
+        n_pass = passes if part == "decode" else max(1, min(passes, 5))
+        seconds, times, kind = reference_sample(m, indices, passes=n_pass, warmup=min(args.warmup, 2))
+        unit, amount = unit_and_amount(part, m, indices)
+        sample = (("layer 0 (QKV, O, Gate/Up, Down)" if len(indices) == 4 else "layer 0 O projection 4096x4096")
+                  + f" at M={m} per step, {n_pass} timed passes")
+        blocks[part] = {"value": amount / seconds, "unit": unit, "ms_per_step": seconds * 1e3,
+                        "stats": summary([t * 1e3 for t in times]),
+                        "cpu_baseline": {"value": amount / seconds, "unit": unit, "sample": sample,
+                                         **cpu_description(kind)},
+                        "e2e": {"value": amount / seconds, "unit": unit, "h2d_bytes_per_step": 0,
+                                "d2h_bytes_per_step": 0}}
+    head = blocks.get("decode") or blocks["prefill"]
+    line.update({"value": head["value"], "unit": head["unit"], "ms_per_step": head["ms_per_step"],
+                 "stats": head["stats"], "cpu_baseline": head["cpu_baseline"], "e2e": head["e2e"]})
+    if workload == "stack":
+        line["gemm"] = blocks["prefill"]
     print(json.dumps(line), flush=True)
 
 
 # ------------------------------------------------------------------------------------------------
 # Our arm
 # ------------------------------------------------------------------------------------------------
-def check_parity(actual, expected, what):
+def parity_numbers(actual, expected):
     a, e = actual.float().cpu(), expected.float().cpu()
     rel = ((a - e).norm() / e.norm().clamp_min(1e-30)).item()
     worst = ((a - e).abs() - (1e-2 + 1e-2 * e.abs())).max().item()
+    return rel, worst
+
+
+def check_parity(actual, expected, what):
+    rel, worst = parity_numbers(actual, expected)
     if not (rel <= 1e-3 and worst <= 0):
         raise SystemExit(f"parity failure on {what}: rel L2 {rel:.3e}, element excess {worst:.3e}")
     return rel
@@ -310,270 +404,549 @@ def leave_process_group(world):
     os._exit(0)
 
 
-def run_ours(args):
-    import torch.distributed as dist
+class Context:
+    """What every workload of our arm needs: ranks, device, peaks, the clock sampler."""
 
-    world = int(os.environ.get("WORLD_SIZE", "1"))
-    rank = int(os.environ.get("RANK", "0"))
-    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
-    if not torch.cuda.is_available():
-        raise SystemExit("bench.py needs a CUDA GPU; there is no CPU fallback")
-    torch.cuda.set_device(local_rank)
-    device = torch.device("cuda", local_rank)
+    def __init__(self, args):
+        import torch.distributed as dist
+
+        self.args = args
+        self.world = int(os.environ.get("WORLD_SIZE", "1"))
+        self.rank = int(os.environ.get("RANK", "0"))
+        self.local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+        if not torch.cuda.is_available():
+            raise SystemExit("bench.py needs a CUDA GPU; there is no CPU fallback")
+        torch.cuda.set_device(self.local_rank)
+        self.device = torch.device("cuda", self.local_rank)
+        if self.world > 1:
+            import datetime
+            dist.init_process_group("nccl", timeout=datetime.timedelta(seconds=300))
+        if self.world != args.gpus:
+            raise SystemExit(f"--gpus {args.gpus} but WORLD_SIZE={self.world}; launch with torchrun for N > 1")
+        from lowbitlinear_b200._extension import load_cuda_extension
+
+        load_cuda_extension(required=True)  # fail loudly without the native library
+        torch.backends.cuda.matmul.allow_tf32 = False
+        self.peaks = measured_peaks()
+        self.dist = dist
+        self.sampler = ClockSampler(self.local_rank) if self.rank == 0 else None
+
+    def barrier(self):
+        if self.world > 1:
+            self.dist.barrier()
+        torch.cuda.synchronize()
+
+    def max_over_ranks(self, value):
+        if self.world == 1:
+            return value
+        t = torch.tensor([value], device=self.device, dtype=torch.float64)
+        self.dist.all_reduce(t, op=self.dist.ReduceOp.MAX)
+        return t.item()
+
+    def timed_replays(self, replay, steps, warmup):
+        """`warmup` untimed replays, then exactly `steps` replays, each between its own CUDA events
+        on the launching stream, bracketed by barrier + synchronize.  Returns (total ms as the
+        maximum over ranks, this rank's per-step ms, clock record of the region)."""
+        for _ in range(max(warmup, 3)):
+            replay()
+        self.barrier()
+        events = [torch.cuda.Event(enable_timing=True) for _ in range(steps + 1)]
+        self.barrier()
+        t0 = time.perf_counter()
+        events[0].record()
+        for i in range(steps):
+            replay()
+            events[i + 1].record()
+        self.barrier()
+        t1 = time.perf_counter()
+        total = self.max_over_ranks(events[0].elapsed_time(events[-1]))
+        per_step = [events[i].elapsed_time(events[i + 1]) for i in range(steps)]
+        clocks = self.sampler.window(t0, t1) if self.sampler is not None else None
+        return total, per_step, clocks
+
+    def wall_steps(self, step, steps):
+        """End-to-end timing by the host clock (copies included), maximum over ranks."""
+        for _ in range(3):
+            step()
+        self.barrier()
+        t0 = time.perf_counter()
+        for _ in range(steps):
+            step()
+        self.barrier()
+        return self.max_over_ranks((time.perf_counter() - t0) * 1e3 / steps)
+
+
+def reference_layer0(ctx):
+    """Rank 0 runs the reference's CPU path on layer 0 (M = 1) in a process of its own -- the
+    reference install registers the same operator names as this library, so the two never share
+    a process -- and every rank receives its inputs and outputs."""
+    payload = [None]
+    if ctx.rank == 0:
+        with tempfile.TemporaryDirectory() as tmp:
+            emit = str(Path(tmp) / "layer0.npz")
+            env = {k: v for k, v in os.environ.items() if k != "OMP_NUM_THREADS"}
+            env.update(RANK="0", WORLD_SIZE="1")
+            timed = ctx.world == 1  # the timed CPU baseline is reported at N = 1 only
+            result = subprocess.run([sys.executable, str(ROOT / "bench.py"), "--impl", "reference", "--emit", emit,
+                                     "--steps", "3" if timed else "1", "--warmup", "1" if timed else "0"],
+                                    capture_output=True, text=True, env=env)
+            if result.returncode != 0:
+                raise SystemExit("the CPU reference leg failed:\n" + result.stdout[-2000:] + result.stderr[-2000:])
+            info = json.loads(result.stdout.strip().splitlines()[-1])
+            data = np.load(emit)
+            payload[0] = (info, {key: data[key] for key in data.files})
+    if ctx.world > 1:
+        ctx.dist.broadcast_object_list(payload, src=0)
+    info, arrays = payload[0]
+    tensors = {key: torch.from_numpy(value) for key, value in arrays.items()}
+    host_layer0 = [(tensors[f"packed{i}"], tensors[f"scales{i}"], tensors[f"zeros{i}"]) for i in range(4)]
+    host_x0 = [tensors[f"x{i}"] for i in range(4)]
+    expected = [tensors[f"y{i}"] for i in range(4)]
+    return info, host_layer0, host_x0, expected
+
+
+def check_layer0(ctx, layers, runner, expected, m_label):
+    """Every rank compares its layer-0 outputs of `runner` with the CPU reference (its own
+    column block for the N-split linears, the whole all-reduced vector for Down), and the ranks
+    compare their Down outputs bit for bit.  Returns {name: worst relative L2 over the ranks}."""
+    result = {}
+    for idx, (name, n, k) in enumerate(SHAPES):
+        got = runner.ys[idx]
+        want = expected[idx]
+        if ctx.world > 1 and name != "down":
+            cols = n // ctx.world
+            want = want[:, ctx.rank * cols:(ctx.rank + 1) * cols]
+        rel = check_parity(got, want, f"layer 0 {name} ({m_label}) vs the CPU reference, rank {ctx.rank}")
+        result[name] = ctx.max_over_ranks(rel)
+        if ctx.world > 1 and name == "down":
+            gathered = [torch.empty_like(got) for _ in range(ctx.world)]
+            ctx.dist.all_gather(gathered, got.contiguous())
+            if not all(torch.equal(gathered[0], other) for other in gathered[1:]):
+                raise SystemExit("ranks disagree on an all-reduced Down output")
+            result["down_bit_identical_across_ranks"] = True
+    return result
+
+
+def run_decode(ctx, layers, reference):
+    """M = 1: the whole stack as one grouped launch (plus the all-reduce kernel between ranks)."""
+    from lowbitlinear_b200 import _ops
+    from lowbitlinear_b200.graph import GraphedLinears
+
+    args, world, device = ctx.args, ctx.world, ctx.device
+    info, _, host_x0, expected = reference
+    exchange = None
     if world > 1:
-        import datetime
-        dist.init_process_group("nccl", timeout=datetime.timedelta(seconds=180))
-    if world != args.gpus:
-        raise SystemExit(f"--gpus {args.gpus} but WORLD_SIZE={world}; launch with torchrun for N > 1")
+        from lowbitlinear_b200.tensor_parallel import PeerExchange
+        exchange = PeerExchange(max_n=LAYERS * SHAPES[3][1], device=device)
+    reduce = [name == "down" for name, _ in layers]
+    modules = [layer for _, layer in layers]
+    runner = GraphedLinears(modules, m=1, reduce=reduce, exchange=exchange)
+    assert runner.grouped
+    fill_activations(runner, layers, 1, device, ctx.rank, world, host_x0)
+    note("decode: correctness")
+    runner.replay()
+    torch.cuda.synchronize()
+    parity = check_layer0(ctx, layers, runner, expected, "M=1, grouped launch")
+    # The public per-call API on the same inputs: identical arithmetic, so identical bits wherever
+    # that call does not split K; other layers against an FP32 evaluation on the GPU.
+    for i in (1, 5, 70, 143):
+        name, layer = layers[i]
+        if world > 1 and name == "down":
+            continue
+        eager = layer(runner.xs[i])
+        if _ops.select_path(1, layer.out_features, layer.in_features, 0) == _ops.PATH_GEMV:
+            if not torch.equal(eager, runner.ys[i]):
+                raise SystemExit(f"grouped launch differs from QuantizedLinear.forward on linear {i}")
+        kk = layer.in_features
+        shifts = torch.arange(8, device=device) * 4
+        q = ((layer.packed_weight.to(torch.int64)[..., None] >> shifts) & 15).reshape(layer.out_features, -1)[:, :kk]
+        groups = torch.arange(kk, device=device) // 64
+        w = (q.float() - layer.zeros[:, groups].float()) * layer.scales[:, groups]
+        check_parity(runner.ys[i], (runner.xs[i].float() @ w.T).half(), f"linear {i} ({name}) vs FP32 torch")
+        del q, w
 
+    note("decode: timed region")
+    total_ms, per_step, clocks = ctx.timed_replays(runner.replay, args.steps, args.warmup)
+    ms_per_step = total_ms / args.steps
+    after = runner.y_flat.clone()
+    runner.replay()
+    torch.cuda.synchronize()
+    if not torch.equal(after, runner.y_flat):
+        raise SystemExit("the grouped launch is not bit-reproducible")
+
+    # ---- end to end: pinned host activations -> device -> one replay -> host outputs --------------
+    host_x = runner.x_flat.cpu().pin_memory()
+    host_y = torch.zeros(runner.y_flat.numel(), dtype=torch.float16).pin_memory()
+    e2e_ms = ctx.wall_steps(lambda: runner.run(host_x, host_y), max(5, min(args.steps, 50)))
+    if not torch.equal(host_y, after.cpu()):
+        raise SystemExit("end-to-end outputs differ from the device-timed ones")
+
+    # ---- secondary: one launch per linear (what a model with dependent layers would do) -----------
+    per_linear = None
+    if world == 1:
+        plain = GraphedLinears(modules, m=1, grouped=False)
+        plain.x_flat.copy_(runner.x_flat)
+        plain_total, plain_steps, _ = ctx.timed_replays(plain.replay, min(args.steps, 20), 3)
+        plain_ms = plain_total / min(args.steps, 20)
+        eager_ms = None
+        steps = 3
+        xs = plain.xs
+        for _ in range(2):
+            for layer, x in zip(modules, xs):
+                layer(x)
+        torch.cuda.synchronize()
+        t0 = time.perf_counter()
+        for _ in range(steps):
+            for layer, x in zip(modules, xs):
+                layer(x)
+        torch.cuda.synchronize()
+        eager_ms = (time.perf_counter() - t0) * 1e3 / steps
+        per_linear = {"ms_per_step": plain_ms, "launches_per_step": len(modules),
+                      "how": "CUDA graph of 144 launches with programmatic dependent launch",
+                      "eager_forward_ms_per_step": eager_ms}
+        del plain
+
+    status = _ops.device_status(device)
+    if status != 0:
+        raise SystemExit(f"device status {status}: a bounded wait expired inside a kernel")
+
+    unit, per_layer = unit_and_amount("decode", 1, [0, 1, 2, 3])
+    amount = per_layer * LAYERS  # whole job, all ranks together
+    value = amount / (ms_per_step * 1e-3)
+    if per_linear is not None:
+        per_linear["value"] = amount / (per_linear["ms_per_step"] * 1e-3)
+        per_linear["unit"] = unit
+    launches = 1 if world == 1 else 2
+    algorithmic_per_launch = amount * 1e9 / world
+    ratio, source = traffic_ratio("w4a16_gemv_grouped_kernel")
+    roofline = {"bound": "hbm", "achieved": value / world, "peak": ctx.peaks["hbm_gbs"], "unit": "GB/s",
+                "frac": value / world / ctx.peaks["hbm_gbs"],
+                "traffic": None if ratio is None else ratio * algorithmic_per_launch,
+                "traffic_unit": "DRAM bytes (read + write) per launch", "traffic_source": source,
+                "kernel": "w4a16_gemv_grouped_kernel", "peak_source": ctx.peaks["source"],
+                "algorithmic_bytes_per_launch": algorithmic_per_launch,
+                "per_launch": "one launch per step: this GPU's algorithmic bytes of the step over the step's CUDA-event time",
+                "fraction_of_nominal_8tbs": value / world / 8000.0}
+    block = {"value": value, "unit": unit, "ms_per_step": ms_per_step, "stats": summary(per_step),
+             "roofline": roofline, "clocks": clocks,
+             "e2e": {"value": amount / (e2e_ms * 1e-3), "unit": unit, "ms_per_step": e2e_ms,
+                     "h2d_bytes_per_step": int(host_x.numel() * 2), "d2h_bytes_per_step": int(host_y.numel() * 2),
+                     "api": "lowbitlinear_b200.graph.GraphedLinears.run: pinned host activations in, one CUDA-graph "
+                            "replay (one grouped launch), host outputs out"},
+             "gpu_launches": launches * args.steps,
+             "launch": ("one grouped launch (lbl_w4a16_group_run) over the 144 independent linears"
+                        + ("" if world == 1 else " + one all-reduce kernel over NVLink peer memory for the 36 Down outputs")),
+             "per_linear_launch": per_linear,
+             "parity": {"rel_l2_vs_cpu_reference": parity, "tolerance": TOLERANCE, "checker": info["kind"]}}
+    return block, runner, exchange
+
+
+def run_prefill(ctx, layers, reference):
+    """M = 2048: one launch per linear (TMA + tcgen05 GEMM); NCCL all-reduce of Down between ranks."""
+    from lowbitlinear_b200 import _ops
+    from lowbitlinear_b200.graph import GraphedLinears
+
+    args, world, device = ctx.args, ctx.world, ctx.device
+    m = PREFILL_M
+    reduce = [name == "down" for name, _ in layers]
+    modules = [layer for _, layer in layers]
+    runner = GraphedLinears(modules, m=m, reduce=reduce)
+    fill_activations(runner, layers, m, device, ctx.rank, world, None)
+    # Layer 0: rows 0..3 of every activation are the CPU reference's M = 1 activations, so the
+    # reference outputs of the decode leg check the GEMM as well.
+    _, _, host_x0, expected = reference
+    for idx, (name, n, k) in enumerate(SHAPES):
+        x = host_x0[idx]
+        if world > 1 and name == "down":
+            part = layers[idx][1].in_features
+            x = x[:, ctx.rank * part:(ctx.rank + 1) * part]
+        runner.xs[idx][0:1].copy_(x.to(device))
+    note("prefill: correctness")
+    runner.replay()
+    torch.cuda.synchronize()
+    parity = {}
+    for idx, (name, n, k) in enumerate(SHAPES):
+        got = runner.ys[idx][0:1]
+        want = expected[idx]
+        if world > 1 and name != "down":
+            cols = n // world
+            want = want[:, ctx.rank * cols:(ctx.rank + 1) * cols]
+        parity[name] = ctx.max_over_ranks(check_parity(got, want, f"layer 0 {name} (M={m}, row 0) vs the CPU reference"))
+    for i in (6, 75):  # whole outputs of two other linears against an FP32 evaluation on the GPU
+        name, layer = layers[i]
+        if world > 1 and name == "down":
+            continue
+        kk = layer.in_features
+        shifts = torch.arange(8, device=device) * 4
+        q = ((layer.packed_weight.to(torch.int64)[..., None] >> shifts) & 15).reshape(layer.out_features, -1)[:, :kk]
+        groups = torch.arange(kk, device=device) // 64
+        w = (q.float() - layer.zeros[:, groups].float()) * layer.scales[:, groups]
+        check_parity(runner.ys[i], (runner.xs[i].float() @ w.T).half(), f"linear {i} ({name}, M={m}) vs FP32 torch")
+        del q, w
+
+    note("prefill: timed region")
+    total_ms, per_step, clocks = ctx.timed_replays(runner.replay, args.steps, args.warmup)
+    ms_per_step = total_ms / args.steps
+
+    # ---- end to end: one layer at a time through the same pinned buffers (the activations of a
+    # whole step would need 9 GB of pinned memory), so every layer is fed layer 0's activation
+    # values; work and bytes moved per step are unchanged.
+    chunk = len(SHAPES)
+    x_elems = sum(runner.xs[i].numel() for i in range(chunk))
+    y_elems = sum(runner.ys[i].numel() for i in range(chunk))
+    host_x = torch.empty(x_elems, dtype=torch.float16).pin_memory()
+    host_x.copy_(torch.cat([runner.xs[i].reshape(-1) for i in range(chunk)]).cpu())
+    host_y = torch.empty(y_elems, dtype=torch.float16).pin_memory()
+    dev_x = torch.empty(x_elems, dtype=torch.float16, device=device)
+    dev_y = torch.empty(y_elems, dtype=torch.float16, device=device)
+    x_views, y_views, xo, yo = [], [], 0, 0
+    for i in range(chunk):
+        x_views.append(dev_x[xo:xo + runner.xs[i].numel()].view_as(runner.xs[i]))
+        y_views.append(dev_y[yo:yo + runner.ys[i].numel()].view_as(runner.ys[i]))
+        xo += runner.xs[i].numel()
+        yo += runner.ys[i].numel()
+    scratch = runner.scratch
+
+    def e2e_step():
+        for c in range(LAYERS):
+            dev_x.copy_(host_x, non_blocking=True)
+            for j in range(chunk):
+                name, layer = layers[c * chunk + j]
+                _ops.linear_out(x_views[j], layer.packed_weight, layer.scales, layer.zeros, y_views[j],
+                                workspace=scratch)
+                if world > 1 and name == "down":
+                    ctx.dist.all_reduce(y_views[j])
+            host_y.copy_(dev_y, non_blocking=True)
+        torch.cuda.current_stream().synchronize()
+
+    e2e_ms = ctx.wall_steps(e2e_step, max(2, min(args.steps, 5)))
+    status = _ops.device_status(device)
+    if status != 0:
+        raise SystemExit(f"device status {status}: a bounded wait expired inside a kernel")
+
+    unit, per_layer = unit_and_amount("prefill", m, [0, 1, 2, 3])
+    amount = per_layer * LAYERS
+    value = amount / (ms_per_step * 1e-3)
+    ratio, source = traffic_ratio("w4a16_gemm_tc_kernel")
+    algorithmic_per_launch = sum(linear_bytes(m, n, k) for _, n, k in SHAPES) / 4.0 / world
+    roofline = {"bound": "tensor", "achieved": value / world, "peak": ctx.peaks["tflops_sustained"], "unit": "TFLOP/s",
+                "frac": value / world / ctx.peaks["tflops_sustained"],
+                "traffic": None if ratio is None else ratio * algorithmic_per_launch,
+                "traffic_unit": "DRAM bytes (read + write) per average launch", "traffic_source": source,
+                "kernel": "w4a16_gemm_tc_kernel", "peak_source": ctx.peaks["source"] + " (sustained bf16 GEMM)",
+                "per_launch": "this GPU's flops of the step / 144 launches over the step's CUDA-event time / 144",
+                "fraction_of_nominal_2250": value / world / 2250.0}
+    block = {"metric": metric_name("prefill"), "value": value, "unit": unit, "ms_per_step": ms_per_step,
+             "stats": summary(per_step), "roofline": roofline, "clocks": clocks,
+             "e2e": {"value": amount / (e2e_ms * 1e-3), "unit": unit, "ms_per_step": e2e_ms,
+                     "h2d_bytes_per_step": int(x_elems * 2 * LAYERS), "d2h_bytes_per_step": int(y_elems * 2 * LAYERS),
+                     "api": "lowbitlinear_b200._ops.linear_out per linear, eager, one layer's pinned host activations "
+                            "in and host outputs out at a time"},
+             "gpu_launches": len(layers) * args.steps,
+             "launch": "CUDA graph of 144 launches" + ("" if world == 1 else " with 36 NCCL all-reduces"),
+             "parity": {"rel_l2_vs_cpu_reference": parity, "tolerance": TOLERANCE}}
+    return block
+
+
+def run_stack(args):
+    ctx = Context(args)
+    with torch.inference_mode():
+        note("CPU reference leg")
+        reference = reference_layer0(ctx)
+        info = reference[0]
+        note("building the stack")
+        layers = build_layers(ctx.device, ctx.rank, ctx.world, reference[1])
+        torch.cuda.synchronize()
+        decode = prefill = None
+        if args.workload in ("stack", "decode"):
+            decode, runner, exchange = run_decode(ctx, layers, reference)
+            del runner
+        if args.workload in ("stack", "prefill"):
+            prefill = run_prefill(ctx, layers, reference)
+    if ctx.sampler is not None:
+        ctx.sampler.close()
+    if ctx.rank != 0:
+        leave_process_group(ctx.world)
+        return
+    head = decode if decode is not None else prefill
+    unit, amount = unit_and_amount("decode", 1, [0, 1, 2, 3])
+    cpu_baseline = {"value": amount / info["seconds_per_pass"], "unit": unit,
+                    "sample": f"layer 0 (QKV, O, Gate/Up, Down) at M=1, {len(info['times'])} passes of "
+                              f"{info['seconds_per_pass']:.2f} s", **{k: info[k] for k in
+                                                                     ("kind", "cores", "cpu_count", "cpu_model", "implementation")}}
+    line = {"metric": metric_name(args.workload), "value": head["value"], "unit": head["unit"], "n_gpus": ctx.world,
+            "steps": args.steps, "warmup": max(args.warmup, 3), "ms_per_step": head["ms_per_step"],
+            "higher_is_better": True, "scaling": "strong", "vs_baseline": None,
+            "dtype": "f16 activations x int4 weights, f32 accumulate", "data": "synthetic",
+            "config": config_of(args.workload, ctx.world)}
+    for key in ("stats", "roofline", "clocks", "e2e", "gpu_launches", "launch", "per_linear_launch", "parity"):
+        if key in head:
+            line[key] = head[key]
+    line["cpu_baseline"] = cpu_baseline if ctx.world == 1 else None
+    if decode is not None and prefill is not None:
+        line["gemm"] = prefill
+    print(json.dumps(line), flush=True)
+    leave_process_group(ctx.world)
+
+
+# ------------------------------------------------------------------------------------------------
+# Kernel tables: crossover (config 3) and prefill sweep (config 4), single GPU
+# ------------------------------------------------------------------------------------------------
+def time_rotating(call, copies, replays, device):
+    """µs per call of `call(i)` for i over `copies` distinct weight sets, captured back to back
+    in one CUDA graph (programmatic dependent launch on), median over `replays` replays."""
+    side = torch.cuda.Stream(device=device)
+    side.wait_stream(torch.cuda.current_stream(device))
+    with torch.cuda.stream(side):
+        for i in range(copies):
+            call(i)
+    torch.cuda.current_stream(device).wait_stream(side)
+    torch.cuda.synchronize(device)
+    graph = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(graph, stream=side):
+        for i in range(copies):
+            call(i)
+    for _ in range(3):
+        graph.replay()
+    torch.cuda.synchronize(device)
+    samples = []
+    for _ in range(replays):
+        start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        start.record()
+        graph.replay()
+        end.record()
+        torch.cuda.synchronize(device)
+        samples.append(start.elapsed_time(end) * 1e3 / copies)
+    del graph
+    return statistics.median(samples), min(samples)
+
+
+def rotating_weights(n, k, copies, device, seed):
+    from lowbitlinear_b200 import QuantizedLinear
+
+    g = torch.Generator(device=device).manual_seed(seed)
+    base = QuantizedLinear.from_float((torch.randn(n, k, device=device, generator=g) * WEIGHT_STD).half())
+    sets = [(base.packed_weight, base.scales, base.zeros)]
+    for _ in range(copies - 1):
+        sets.append((base.packed_weight.clone(), base.scales.clone(), base.zeros.clone()))
+    return sets
+
+
+def reference_gpu_table(workload):
+    """The reference's own CUDA operators on this GPU, timed in a process of their own."""
+    if not any((REF_DIR / "lowbitlinear").glob("_C*")):
+        return None
+    result = subprocess.run([sys.executable, str(ROOT / "bench.py"), "--impl", "reference_gpu", "--workload", workload],
+                            capture_output=True, text=True)
+    if result.returncode != 0:
+        return {"unavailable": (result.stderr.strip().splitlines() or ["failed"])[-1][:300]}
+    return json.loads(result.stdout.strip().splitlines()[-1])["rows"]
+
+
+def run_tables(args):
     from lowbitlinear_b200 import _ops
     from lowbitlinear_b200._extension import load_cuda_extension
 
-    load_cuda_extension(required=True)  # fail loudly without the native library
-    torch.backends.cuda.matmul.allow_tf32 = False
-    m = 1 if args.workload == "decode" else 2048
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py needs a CUDA GPU; there is no CPU fallback")
+    load_cuda_extension(required=True)
+    device = torch.device("cuda", 0)
+    torch.cuda.set_device(device)
     peaks = measured_peaks()
-
-    # ---- CPU baseline and identical-input parity (rank 0, single GPU) -------------------------
-    cpu_baseline, host_layer0, oracle_out = None, None, None
-    if rank == 0 and world == 1:
-        indices = [0, 1, 2, 3] if args.workload == "decode" else [1]
-        seconds, host_layer0_map, oracle_out = oracle_sample(m, indices)
-        unit, amount = unit_and_amount(args.workload, m, indices)
-        cpu_baseline = {"value": amount / seconds, "unit": unit, "cores": blas_threads(), "kind": "port",
-                        "sample": ("layer 0 (QKV, O, Gate/Up, Down)" if len(indices) == 4 else "layer 0 O projection")
-                        + f" at M={m}, one pass, {seconds:.2f} s of numpy oracle"}
-        if len(indices) == 4:
-            host_layer0 = [host_layer0_map[i] for i in range(4)]
-
+    sampler = ClockSampler(0, period_s=0.02)
+    t_start = time.perf_counter()
+    rows = []
+    _ops.set_programmatic_dependent_launch(True)
     with torch.inference_mode():
-        global EXCHANGE
-        if world > 1 and args.workload == "decode" and args.fused_allreduce:
-            from lowbitlinear_b200.tensor_parallel import PeerExchange
-            EXCHANGE = PeerExchange(max_n=4096, device=device)
-        note("building the stack")
-        layers, xs = build_stack(m, device, rank, world, host_layer0)
-        torch.cuda.synchronize()
+        if args.workload == "crossover":
+            paths = [("gemv", _ops.PATH_GEMV), ("gemm_tc_small", _ops.PATH_GEMM_TC_SMALL),
+                     ("gemm_tc", _ops.PATH_GEMM_TC), ("dispatcher", _ops.PATH_AUTO)]
+            for idx, (name, n, k) in enumerate(SHAPES):
+                copies = max(3, -(-(300 << 20) // linear_bytes(1, n, k)))  # > 2 x L2 of weights in rotation
+                sets = rotating_weights(n, k, copies, device, seed=idx)
+                for m in (1, 2, 4, 8, 16, 32, 64):
+                    g = torch.Generator(device=device).manual_seed(100 + m)
+                    x = torch.randn(m, k, device=device, generator=g).half()
+                    row = {"shape": name, "N": n, "K": k, "M": m, "algorithmic_bytes": linear_bytes(m, n, k),
+                           "hbm_ideal_us": linear_bytes(m, n, k) / peaks["hbm_gbs"] / 1e3}
+                    for label, path in paths:
+                        if path == _ops.PATH_GEMV and m > 32:
+                            continue
+                        taken = []
 
-        # ---- correctness before timing -----------------------------------------------------------
-        _ops.set_programmatic_dependent_launch(False)
-        note("eager pass")
-        eager = run_stack(layers, xs, world)
-        torch.cuda.synchronize()
-        parity = {}
-        if oracle_out is not None:
-            for idx, expected in oracle_out.items():
-                if host_layer0 is not None:
-                    parity[SHAPES[idx][0]] = check_parity(eager[idx], expected, f"layer 0 {SHAPES[idx][0]} vs oracle")
-            if host_layer0 is not None:
-                # Packed weights and zero points: the package's quantiser against the oracle's, bit exact.
-                from lowbitlinear_b200.quantization import pack_int4, quantize_int4
-                x_o, w_o = cpu_layer_inputs(m, 1)
-                q, s, z = quantize_int4(w_o, 64)
-                assert torch.equal(pack_int4(q), host_layer0[1][1]) and torch.equal(z, host_layer0[1][3])
-                assert torch.equal(s, host_layer0[1][2])
-        if world == 1:
-            # A few linears of other layers against an FP32 evaluation on the GPU.
-            for i in (5, 70, 143):
-                name, layer = layers[i]
-                kk = layer.in_features
-                shifts = torch.arange(8, device=device) * 4
-                q = ((layer.packed_weight.to(torch.int64)[..., None] >> shifts) & 15).reshape(layer.out_features, -1)[:, :kk]
-                groups = torch.arange(kk, device=device) // 64
-                w = (q.float() - layer.zeros[:, groups].float()) * layer.scales[:, groups]
-                check_parity(eager[i], (xs[i].float() @ w.T).half(), f"linear {i} ({name}) vs FP32 torch")
-                del q, w
+                        def call(i, path=path, taken=taken):
+                            y, t = _ops.linear_forced(x, *sets[i], path, op=0 if m == 1 else 1)
+                            taken.append(t)
+                        us, best = time_rotating(call, copies, args.steps if args.steps != 200 else 30, device)
+                        row[label] = {"us": us, "min_us": best, "gbs": linear_bytes(m, n, k) / us / 1e3,
+                                      "frac_of_hbm": linear_bytes(m, n, k) / us / 1e3 / peaks["hbm_gbs"],
+                                      "path": _ops.PATH_NAMES[taken[0]]}
+                    forced = {k2: v["us"] for k2, v in row.items() if isinstance(v, dict) and k2 != "dispatcher"}
+                    row["dispatcher_is_fastest"] = row["dispatcher"]["us"] <= 1.03 * min(forced.values())
+                    rows.append(row)
+                del sets
+        else:
+            for idx, (name, n, k) in ((2, SHAPES[2]), (3, SHAPES[3])):
+                sets = rotating_weights(n, k, 3, device, seed=idx)
+                for m in (128, 512, 2048, 8192):
+                    g = torch.Generator(device=device).manual_seed(100 + m)
+                    x = torch.randn(m, k, device=device, generator=g).half()
+                    out = torch.empty(m, n, dtype=torch.float16, device=device)
+                    scratch = torch.zeros(max(16, _ops._lib.lbl_w4a16_workspace_bytes(m, n, k, _ops.PATH_AUTO)),
+                                          dtype=torch.uint8, device=device)
 
-        # ---- capture one step as a CUDA graph ---------------------------------------------------
-        note("capturing the step")
-        # When tensor-parallel ranks use NCCL, the kernels alternate with NCCL kernels; a
-        # dependent launch that holds SM resources while it waits for a collective could starve
-        # it, so programmatic dependent launch is used only when no NCCL kernel is in the graph.
-        use_pdl = bool(args.pdl) and (world == 1 or EXCHANGE is not None)
-        _ops.set_programmatic_dependent_launch(use_pdl)
-        side = torch.cuda.Stream()
-        side.wait_stream(torch.cuda.current_stream())
-        with torch.cuda.stream(side):
-            for _ in range(2):
-                run_stack(layers, xs, world)
-        torch.cuda.current_stream().wait_stream(side)
-        torch.cuda.synchronize()
-        graph = torch.cuda.CUDAGraph()
-        with torch.cuda.graph(graph, stream=side):
-            graph_out = run_stack(layers, xs, world)
-        note("first replay")
-        graph.replay()
-        torch.cuda.synchronize()
-        for i, (a, b) in enumerate(zip(graph_out, eager)):
-            if not torch.equal(a, b):
-                if world > 1 and layers[i][0] == "down":
-                    continue  # all-reduce order may differ between eager and captured runs
-                raise SystemExit(f"graph replay differs from eager run on linear {i}")
-
-        note("timed region")
-
-        def barrier():
-            if world > 1:
-                dist.barrier()
-            torch.cuda.synchronize()
-
-        # ---- device-timed region ------------------------------------------------------------------
-        for _ in range(max(args.warmup, 3)):
-            graph.replay()
-        barrier()
-        sampler = ClockSampler(local_rank) if rank == 0 else None
-        start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-        barrier()
-        t0 = time.perf_counter()
-        start.record()
-        for _ in range(args.steps):
-            graph.replay()
-        end.record()
-        barrier()
-        t1 = time.perf_counter()
-        elapsed_ms = start.elapsed_time(end)
-        if world > 1:
-            t = torch.tensor([elapsed_ms], device=device)
-            dist.all_reduce(t, op=dist.ReduceOp.MAX)
-            elapsed_ms = t.item()
-        if elapsed_ms < 1500.0:
-            # The timed region was too short for nvidia-smi to sample: hold the same load a
-            # little longer, for the clock record only.  Every rank replays the same number of
-            # times (the count derives from the reduced time), since the graph holds collectives.
-            hold_replays = int(1500.0 / max(elapsed_ms / args.steps, 1e-3)) + 1
-            for _ in range(hold_replays):
-                graph.replay()
-            torch.cuda.synchronize()
-            t1 = time.perf_counter()
-        clocks = sampler.stop(t0, t1) if sampler is not None else None
-        ms_per_step = elapsed_ms / args.steps
-
-        note("end-to-end region")
-        # ---- end to end through the public API, host buffers ---------------------------------------
-        _ops.set_programmatic_dependent_launch(False)
-        # Decode: the whole stack's activations go up in one pinned copy and all outputs come
-        # back in one.  Prefill: one layer at a time through the same pinned buffers (the
-        # activations of a step would not fit pinned memory comfortably), so every layer sees
-        # layer 0's activation values; the work per step is unchanged.
-        chunk = len(layers) if args.workload == "decode" else len(SHAPES)
-        x_sizes = [x.numel() for x in xs[:chunk]]
-        host_x = torch.empty(sum(x_sizes), dtype=torch.float16).pin_memory()
-        offset = 0
-        for x, size in zip(xs[:chunk], x_sizes):
-            host_x[offset:offset + size].copy_(x.reshape(-1).cpu())
-            offset += size
-        dev_x = torch.empty_like(host_x, device=device)
-        out_elems = sum(m * layer.out_features for _, layer in layers[:chunk])
-        host_y = torch.empty(out_elems, dtype=torch.float16).pin_memory()
-        chunks_per_step = len(layers) // chunk
-
-        def e2e_step():
-            for c in range(chunks_per_step):
-                dev_x.copy_(host_x, non_blocking=True)
-                views, off = [], 0
-                for x, size in zip(xs[:chunk], x_sizes):
-                    views.append(dev_x[off:off + size].view_as(x))
-                    off += size
-                outs = run_stack(layers[c * chunk:(c + 1) * chunk], views, world)
-                host_y.copy_(torch.cat([o.reshape(-1) for o in outs]), non_blocking=True)
-            torch.cuda.current_stream().synchronize()
-
-        e2e_api = "QuantizedLinear.forward, eager, pinned host activations in, host outputs out"
-        e2e_eager_ms = None
-        if args.workload == "decode" and world == 1:
-            # Eager first (kept as a secondary figure), then the CUDA-graph runner of the package:
-            # one pinned host-to-device copy, one replay of the captured operators, one copy back.
-            for _ in range(2):
-                e2e_step()
-            t_eager = time.perf_counter()
-            for _ in range(5):
-                e2e_step()
-            e2e_eager_ms = (time.perf_counter() - t_eager) * 1e3 / 5
-            from lowbitlinear_b200.graph import GraphedLinears
-            runner = GraphedLinears([layer for _, layer in layers], m=m,
-                                    programmatic_dependent_launch=bool(args.pdl))
-            host_x = torch.zeros(runner.x_flat.numel(), dtype=torch.float16).pin_memory()
-            host_y = torch.zeros(runner.y_flat.numel(), dtype=torch.float16).pin_memory()
-            for offset, x in zip(runner.x_offsets, xs):
-                host_x[offset:offset + x.numel()] = x.reshape(-1).cpu()
-            runner.run(host_x, host_y)
-            for offset, want in zip(runner.y_offsets, eager):
-                if not torch.equal(host_y[offset:offset + want.numel()].view_as(want), want.cpu()):
-                    raise SystemExit("graph runner output differs from the eager forward")
-            chunks_per_step = 1
-
-            def e2e_step():  # noqa: F811
-                runner.run(host_x, host_y)
-
-            e2e_api = ("lowbitlinear_b200.graph.GraphedLinears.run: pinned host activations in, one CUDA-graph "
-                       "replay of the public operators, host outputs out")
-
-        e2e_steps = max(3, min(args.steps, 20))
-        for _ in range(3):
-            e2e_step()
-        barrier()
-        e0 = time.perf_counter()
-        for _ in range(e2e_steps):
-            e2e_step()
-        barrier()
-        e2e_ms = (time.perf_counter() - e0) * 1e3 / e2e_steps
-        if world > 1:
-            t = torch.tensor([e2e_ms], device=device)
-            dist.all_reduce(t, op=dist.ReduceOp.MAX)
-            e2e_ms = t.item()
-
-        status = _ops.device_status(device)
-        if status != 0:
-            raise SystemExit(f"device status {status}: a bounded wait expired inside a kernel")
-
-    # ---- report -------------------------------------------------------------------------------------
-    all_idx = [0, 1, 2, 3]
-    unit, per_layer = unit_and_amount(args.workload, m, all_idx)
-    amount = per_layer * LAYERS  # whole job, all ranks together
-    value = amount / (ms_per_step * 1e-3)
-    launches_per_step = len(layers)
-    # DRAM bytes per launch: ratio of (dram read + write) to algorithmic bytes from the committed
-    # ncu captures of one Gate/Up launch (profiles/), applied to this rank's average launch;
-    # traffic follows the weights in proportion, there are no re-reads.
-    algorithmic_bytes_per_launch = sum(linear_bytes(m, SHAPES[i][1], SHAPES[i][2]) for i in all_idx) / 4.0 / world
-    traffic_ratio = 1.006 if args.workload == "decode" else 0.750
-    traffic = traffic_ratio * algorithmic_bytes_per_launch
-    if args.workload == "decode":
-        roofline = {"bound": "hbm", "achieved": value / world, "peak": peaks["hbm_gbs"], "unit": "GB/s",
-                    "frac": value / world / peaks["hbm_gbs"], "traffic": traffic,
-                    "traffic_unit": "bytes per launch (ncu dram read+write of one Gate/Up launch, scaled)",
-                    "kernel": "w4a16_gemv_decode_kernel", "peak_source": peaks["source"],
-                    "per_launch": "per-GPU algorithmic bytes of the step / 144 launches, over the step's CUDA-event time / 144"}
-    else:
-        roofline = {"bound": "tensor", "achieved": value / world, "peak": peaks["tflops_sustained"], "unit": "TFLOP/s",
-                    "frac": value / world / peaks["tflops_sustained"], "traffic": traffic,
-                    "traffic_unit": "bytes per launch (ncu dram read+write of one Gate/Up launch, scaled)",
-                    "kernel": "w4a16_gemm_tc_kernel", "peak_source": peaks["source"] + " (sustained bf16)",
-                    "per_launch": "per-GPU flops of the step / 144 launches, over the step's CUDA-event time / 144"}
-    if rank != 0:
-        leave_process_group(world)
-        return
-    line = {
-        "metric": metric_name(args.workload), "value": value, "unit": unit, "n_gpus": world,
-        "steps": args.steps, "warmup": max(args.warmup, 3), "ms_per_step": ms_per_step,
-        "higher_is_better": True, "scaling": "strong", "vs_baseline": None,
-        "dtype": "f16 activations x int4 weights, f32 accumulate", "data": "synthetic",
-        "config": dict(config_of(args.workload, m, world, args.pdl and (world == 1 or EXCHANGE is not None)),
-                       allreduce=("none" if world == 1 else
-                                  "fused into the Down GEMV over NVLink peer memory" if EXCHANGE is not None
-                                  else "NCCL")),
-        "roofline": roofline, "cpu_baseline": cpu_baseline, "clocks": clocks,
-        "e2e": {"value": amount / (e2e_ms * 1e-3), "unit": unit, "ms_per_step": e2e_ms,
-                "h2d_bytes_per_step": int(host_x.numel() * 2 * chunks_per_step),
-                "d2h_bytes_per_step": int(host_y.numel() * 2 * chunks_per_step),
-                "api": e2e_api,
-                "eager_forward_ms_per_step": e2e_eager_ms},
-        "gpu_launches": launches_per_step * args.steps,
-        "parity": {"rel_l2_vs_oracle": parity, "tolerance": "rel L2 <= 1e-3, |a-b| <= 1e-2 + 1e-2|b|"},
-        "fraction_of_nominal": value / world / (8000.0 if args.workload == "decode" else 2250.0),
-    }
+                    def call(i):
+                        _ops.linear_out(x, *sets[i], out, op=1, workspace=scratch)
+                    us, best = time_rotating(call, 3, args.steps if args.steps != 200 else 30, device)
+                    flops = linear_flops(m, n, k)
+                    rows.append({"shape": name, "N": n, "K": k, "M": m, "us": us, "min_us": best,
+                                 "tflops": flops / us / 1e6, "frac_of_sustained_bf16": flops / us / 1e6 / peaks["tflops_sustained"],
+                                 "frac_of_nominal_2250": flops / us / 1e6 / 2250.0,
+                                 "path": _ops.PATH_NAMES[_ops.select_path(m, n, k)]})
+                    del out
+                del sets
+    _ops.set_programmatic_dependent_launch(False)
+    status = _ops.device_status(device)
+    if status != 0:
+        raise SystemExit(f"device status {status}: a bounded wait expired inside a kernel")
+    clocks = sampler.window(t_start, time.perf_counter())
+    sampler.close()
+    line = {"workload": args.workload, "n_gpus": 1, "rows": rows, "clocks": clocks, "peaks": peaks,
+            "timing": "CUDA graph of back-to-back launches over rotating weight copies (> 2 x L2), programmatic "
+                      "dependent launch, CUDA events around a replay, median of the replays",
+            "reference_kernels_on_this_gpu": reference_gpu_table(args.workload)}
     print(json.dumps(line), flush=True)
-    leave_process_group(world)
+
+
+def run_reference_gpu(args):
+    """The reference's two CUDA operators (oracle/_ref, compiled for sm_100a) on the table shapes.
+    This process imports the reference package only."""
+    sys.path.insert(0, str(REF_DIR))
+    import lowbitlinear  # noqa: F401  (loads the reference's own extension)
+    from lowbitlinear import QuantizedLinear
+
+    device = torch.device("cuda", 0)
+    rows = []
+    with torch.inference_mode():
+        if args.workload == "crossover":
+            cases = [(name, n, k, m) for name, n, k in SHAPES for m in (1, 2, 4, 8, 16, 32, 64)]
+        else:
+            cases = [(name, n, k, m) for name, n, k in SHAPES[2:] for m in (128, 512, 2048)]
+        cache = {}
+        for name, n, k, m in cases:
+            if (n, k) not in cache:
+                cache.clear()
+                g = torch.Generator(device=device).manual_seed(n + k)
+                base = QuantizedLinear.from_float((torch.randn(n, k, device=device, generator=g) * WEIGHT_STD).half())
+                copies = max(3, -(-(300 << 20) // linear_bytes(1, n, k)))
+                cache[(n, k)] = [base] + [QuantizedLinear(base.packed_weight.clone(), base.scales.clone(),
+                                                          base.zeros.clone(), in_features=k) for _ in range(copies - 1)]
+            layers = cache[(n, k)]
+            x = torch.randn(m, k, device=device).half()
+            us, best = time_rotating(lambda i: layers[i](x), len(layers), 10, device)
+            rows.append({"shape": name, "M": m, "us": us, "min_us": best,
+                         "operator": "w4a16_gemv_warp_vec" if m == 1 else "cute_w4a16 gemm"})
+    print(json.dumps({"impl": "reference_gpu", "rows": rows}), flush=True)
 
 
 def main():
@@ -581,18 +954,23 @@ def main():
     parser.add_argument("--gpus", type=int, default=1)
     parser.add_argument("--steps", type=int, default=200)
     parser.add_argument("--warmup", type=int, default=5)
-    parser.add_argument("--impl", choices=("ours", "reference"), default="ours")
-    parser.add_argument("--workload", choices=("decode", "prefill"), default="decode")
-    parser.add_argument("--pdl", type=int, default=1)
-    parser.add_argument("--fused-allreduce", type=int, default=1,
-                        help="tensor-parallel decode: fuse the K-split all-reduce into the GEMV (0: NCCL)")
+    parser.add_argument("--impl", choices=("ours", "reference", "reference_gpu"), default="ours")
+    parser.add_argument("--workload", choices=("stack", "decode", "prefill", "crossover", "prefill_sweep"),
+                        default="stack")
+    parser.add_argument("--emit", default=None, help=argparse.SUPPRESS)
     args = parser.parse_args()
     if args.impl == "reference":
         if args.steps == 200:
-            args.steps = 3
+            args.steps = 5
         run_reference_arm(args)
+    elif args.impl == "reference_gpu":
+        run_reference_gpu(args)
+    elif args.workload in ("crossover", "prefill_sweep"):
+        run_tables(args)
     else:
-        run_ours(args)
+        if args.steps == 200:
+            args.steps = 50
+        run_stack(args)
 
 
 if __name__ == "__main__":

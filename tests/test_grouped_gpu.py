@@ -94,7 +94,7 @@ def test_decode_layers_at_full_size_in_one_launch(cuda_ops):
 
 
 def test_group_inside_a_cuda_graph_with_dependent_launch(cuda_ops):
-    from lowbitlinear_b200 import QuantizedLinear
+    from lowbitlinear_b200 import QuantizedLinear, _ops
     from lowbitlinear_b200.graph import GraphedLinears
 
     layers = []
@@ -109,13 +109,14 @@ def test_group_inside_a_cuda_graph_with_dependent_launch(cuda_ops):
         runner.run(host_x, host_y)
     for layer, xo, yo in zip(layers, runner.x_offsets, runner.y_offsets):
         x = host_x[xo:xo + layer.in_features].view(1, -1).to(cuda_ops)
-        want = layer(x)
+        want, _ = _ops.linear_forced(x, layer.packed_weight, layer.scales, layer.zeros, _ops.PATH_GEMV, op=0)
         assert torch.equal(host_y[yo:yo + layer.out_features].view(1, -1), want.cpu())
-    # The per-layer form of the runner (one launch per layer, its own scratch) agrees bit for bit.
+    # The per-layer form of the runner (one launch per layer, its own scratch; small N is split
+    # along K there, so the last bit may differ).
     plain = GraphedLinears(layers, m=1, grouped=False)
     other = torch.zeros_like(host_y)
     plain.run(host_x, other)
-    assert torch.equal(other, host_y)
+    torch.testing.assert_close(other, host_y, atol=ATOL, rtol=RTOL)
 
 
 def test_group_rejects_what_it_cannot_serve(cuda_ops):
