@@ -873,9 +873,12 @@ def run_tables(args):
                         if path == _ops.PATH_GEMV and m > 32:
                             continue
                         taken = []
+                        # Scratch of exactly the size this path asks for, owned by this measurement.
+                        need = max(_ops.workspace_bytes(m, n, k, path), _ops.workspace_bytes(m, n, k, _ops.PATH_GEMV_SPLITK))
+                        scratch = torch.zeros(max(16, need), dtype=torch.uint8, device=device)
 
-                        def call(i, path=path, taken=taken):
-                            y, t = _ops.linear_forced(x, *sets[i], path, op=0 if m == 1 else 1)
+                        def call(i, path=path, taken=taken, scratch=scratch):
+                            y, t = _ops.linear_forced(x, *sets[i], path, op=0 if m == 1 else 1, workspace=scratch)
                             taken.append(t)
                         us, best = time_rotating(call, copies, args.steps if args.steps != 200 else 30, device)
                         row[label] = {"us": us, "min_us": best, "gbs": linear_bytes(m, n, k) / us / 1e3,

@@ -261,20 +261,30 @@ def w4a16_gemm(X, packed_w, scales, zeros):
     return Y
 
 
-def linear_forced(X, packed_w, scales, zeros, path, op=1, flags=None):
+def linear_forced(X, packed_w, scales, zeros, path, op=1, flags=None, workspace=None):
     """Runs the dispatcher with a forced kernel path (benchmarks and tests).  Returns
-    ``(Y, path_taken)``; no argument checking beyond what the C ABI does."""
+    ``(Y, path_taken)``; no argument checking beyond what the C ABI does.  ``workspace`` is a
+    zeroed uint8 CUDA tensor of at least ``workspace_bytes(m, n, k, path)`` that the caller owns;
+    without it the per-stream cached scratch is used."""
     m, k = X.shape
     n = packed_w.size(0)
     Y = torch.empty((m, n), dtype=torch.float16, device=X.device)
     stream = _raw_stream(X.device)
     taken = ctypes.c_int(0)
-    _run(X.device, stream, m, n, k, path,
-         lambda ws, ws_bytes: _lib.lbl_w4a16_linear(
-             X.data_ptr(), packed_w.data_ptr(), scales.data_ptr(), zeros.data_ptr(), Y.data_ptr(),
-             m, n, k, op, path, ws, ws_bytes, _flags if flags is None else flags, X.device.index,
-             stream, ctypes.byref(taken)))
+    call = lambda ws, ws_bytes: _lib.lbl_w4a16_linear(
+        X.data_ptr(), packed_w.data_ptr(), scales.data_ptr(), zeros.data_ptr(), Y.data_ptr(),
+        m, n, k, op, path, ws, ws_bytes, _flags if flags is None else flags, X.device.index,
+        stream, ctypes.byref(taken))
+    if workspace is not None:
+        _check(call(workspace.data_ptr(), workspace.numel()))
+    else:
+        _run(X.device, stream, m, n, k, path, call)
     return Y, taken.value
+
+
+def workspace_bytes(m, n, k, path=PATH_AUTO):
+    """Bytes of scratch the given path wants for this problem (``lbl_w4a16_workspace_bytes``)."""
+    return _lib.lbl_w4a16_workspace_bytes(m, n, k, path)
 
 
 def linear_out(X, packed_w, scales, zeros, out, op=None, workspace=None):

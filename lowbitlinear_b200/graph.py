@@ -50,7 +50,8 @@ class GraphedLinears:
         if any(self.reduce):
             import torch.distributed as dist
 
-            world = dist.get_world_size(group)
+            if dist.is_available() and dist.is_initialized():
+                world = dist.get_world_size(group)
         self.world = world
         # Offsets are multiples of 8 elements so that every view stays 16-byte aligned.
         pad = lambda v: (v + 7) // 8 * 8
