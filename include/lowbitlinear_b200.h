@@ -46,6 +46,9 @@ extern "C" {
 #define LBL_PATH_GEMM_TC_SMALL 5 /* tcgen05 GEMM for M <= 128: weights on the M side of the MMA,
                                     K cut into slices (uses the scratch when there is one)   */
 
+#define LBL_PATH_GEMM_WT 6       /* tcgen05 GEMM, weights dequantised in registers and handed to the
+                                    MMA through tensor memory (any M; K sliced when M is small)  */
+
 /* Flags. */
 #define LBL_FLAG_PDL 1u            /* programmatic dependent launch: weights are prefetched
                                       before the previous kernel in the stream has finished.

@@ -14,7 +14,7 @@ import threading
 
 import torch
 
-PATH_AUTO, PATH_GENERIC, PATH_GEMV, PATH_GEMV_SPLITK, PATH_GEMM_TC, PATH_GEMM_TC_SMALL = range(6)
+PATH_AUTO, PATH_GENERIC, PATH_GEMV, PATH_GEMV_SPLITK, PATH_GEMM_TC, PATH_GEMM_TC_SMALL, PATH_GEMM_WT = range(7)
 PATH_NAMES = {
     PATH_AUTO: "auto",
     PATH_GENERIC: "generic",
@@ -22,6 +22,7 @@ PATH_NAMES = {
     PATH_GEMV_SPLITK: "gemv_splitk",
     PATH_GEMM_TC: "gemm_tc",
     PATH_GEMM_TC_SMALL: "gemm_tc_small",
+    PATH_GEMM_WT: "gemm_wt",
 }
 FLAG_PDL = 1
 FLAG_ROUND_WEIGHTS = 2

@@ -222,6 +222,14 @@ int run_linear(const void* X, const int32_t* packed_w, const float* scales, cons
                                       info.sm_count, (flags & LBL_FLAG_PDL) != 0);
       break;
     }
+    case LBL_PATH_GEMM_WT: {
+      if (!lbl::gemm_wt_supports(M, N, K)) {
+        return fail(LBL_ERR_UNSUPPORTED, "tensor-memory GEMM cannot serve M=%lld N=%lld K=%lld (needs N %% 128 == 0, K %% 256 == 0)", (long long)M, (long long)N, (long long)K);
+      }
+      err = lbl::launch_gemm_wt(prob, info.status_word, cu_stream, workspace, workspace_bytes, info.sm_count,
+                                (flags & LBL_FLAG_PDL) != 0);
+      break;
+    }
     default:
       return fail(LBL_ERR_INVALID, "unknown path %d", path);
   }
@@ -263,6 +271,7 @@ size_t lbl_w4a16_workspace_bytes(int64_t M, int64_t N, int64_t K, int path) {
     if (path == LBL_PATH_AUTO) path = select_path(M, N, K, 0, sms);
   }
   if (path == LBL_PATH_GEMM_TC_SMALL) return lbl::gemm_tc_small_workspace_bytes(M, N, K, sms);
+  if (path == LBL_PATH_GEMM_WT) return lbl::gemm_wt_workspace_bytes(M, N, K, sms);
   if (path != LBL_PATH_GEMV && path != LBL_PATH_GEMV_SPLITK) return 0;
   lbl::SkinnyPlan plan;
   const int want = path == LBL_PATH_GEMV_SPLITK ? 2 : -1;

@@ -1,0 +1,539 @@
+// W4A16 GEMM for sm_100a with the weights on the M side of the tcgen05 MMA and passed to it through
+// tensor memory: the dequantised weights never touch shared memory.
+//
+//   Y[M,N] = fp16( X[M,K] . W^T ),   W[n,k] = fp16( float(q[n,k] - zero[n,k/64]) * scale[n,k/64] )
+//
+// (the operand policy of the reference GEMM, csrc/cute_w4a16_gemm.cu:150-165, bit for bit).
+// A CTA owns 256 weight rows (two blocks of 128 = the M of the MMA), BT tokens (16..192, the N of
+// the MMA) and a slice of K, and computes the transposed tiles
+//
+//   D_b[128 weight rows, BT tokens] += W_b[128, 64] . X[BT, 64]^T      b = 0, 1, per k-block of 64
+//
+// with FP32 accumulators in tensor memory.  What moves where:
+//
+//   warp 0      one thread issues the copies.  Per k-block a tiled TMA load of the X block (BT rows
+//               x 64 columns, 128-byte swizzle, rows past M zero-filled) and one of the packed
+//               words of the 256 rows (32 bytes each, landing with a 48-byte pitch: the box is
+//               wider than the tensor's inner extent, the pad is zero-filled and free); per four
+//               k-blocks the rows' four scales and four zero points.  The ring is deep (five to
+//               eight stages): a stage is 36 KB at most because no dequantised tile lives here.
+//   warps 2-9   one thread per weight row: 32 bytes of packed words from shared memory, the exact
+//               dequantisation (tc_common.cuh) of its 64 weights of the k-block in registers, and
+//               one tcgen05.st of the 32 registers into the row's lane of the A operand in tensor
+//               memory (lane = weight row, a column = two consecutive FP16 along K).  No swizzled
+//               shared-memory stores, no proxy fence.
+//   warp 1      one thread issues, per k-block, 4 (K = 16) x 2 (block) tcgen05.mma with A in tensor
+//               memory and B = the X block in shared memory; tcgen05.commit frees the X stage and
+//               the A slot.
+//   warps 2-9   epilogue: tcgen05.ld of the accumulators, lane = weight row, so that for each token
+//               a warp stores 32 neighbouring outputs; or, when K is cut into slices (few tokens,
+//               few row blocks), FP32 partial tiles to the scratch and an ordered addition by the
+//               CTA that draws the row block's last ticket (bit-reproducible).
+//
+// Tensor memory (512 columns): two accumulators of BT columns, then A slots of 32 columns per
+// block (two slots at BT = 192, up to four below).  Shared-memory traffic per k-block is the X
+// block written once and read twice; the tile in gemm_tc.cu writes and reads 64 KB more.
+// Every wait on an mbarrier is bounded; a timeout sets the device status word and the CTA drains.
+// Shapes: N % 128 == 0, K % 256 == 0, any M >= 1.  No cluster launch, no multicast.
+#include "kernels.h"
+#include "tc_common.cuh"
+#include "tensor_map.h"
+
+namespace lbl {
+namespace {
+
+constexpr int kRowsW = 256;     // weight rows per CTA: two MMA blocks of 128
+constexpr int kBK = 64;
+constexpr int kMaxTokens = 192;
+constexpr int kMaxStages = 8;
+constexpr int kMaxASlots = 4;
+constexpr int kDequantWarps = 8;
+constexpr int kThreads = 32 * (2 + kDequantWarps);
+constexpr int kTmemCols = 512;
+constexpr int kPackedPitch = 48;                     // bytes per row of a packed tile in shared memory
+constexpr int kPackedTileBytes = kRowsW * kPackedPitch;  // 12 KB (8 KB of them copied)
+constexpr int kMetaTileBytes = kRowsW * 16;          // four scales or four zero points per row
+constexpr int kMetaSlotBytes = 2 * kMetaTileBytes;
+constexpr int kBarrierBytes = 512;
+constexpr int kSmemBudget = 220 * 1024;
+constexpr int kStatusWtWait = 400;
+constexpr int kMaxSlices = 8;
+
+struct Barriers {
+  uint64_t full[kMaxStages];     // X block and packed words of the stage have landed
+  uint64_t x_empty[kMaxStages];  // the MMAs have read the X block
+  uint64_t w_empty[kMaxStages];  // the dequantisation warps hold the packed words in registers
+  uint64_t meta_full[2];
+  uint64_t meta_empty[2];
+  uint64_t a_full[kMaxASlots];   // the A slot holds the dequantised k-block
+  uint64_t a_empty[kMaxASlots];  // the MMAs have read the A slot
+  uint64_t acc_full;
+  uint32_t tmem_base;
+  int abort_flag;
+  int ticket;
+};
+static_assert(sizeof(Barriers) <= kBarrierBytes, "barrier block too large");
+
+struct WtParams {
+  __half* y;
+  int M, N, K;
+  int tokens;    // BT
+  int m_tiles;   // ceil(M / BT)
+  int slices;    // pieces of K per tile (1 unless m_tiles == 1)
+  int stages;    // depth of the shared-memory ring
+  int a_slots;   // A slots per block in tensor memory
+  float* partials;  // [n_block][slice][M][256] FP32 when slices > 1
+  int* tickets;     // one per row block
+  int* status;
+};
+
+__device__ __forceinline__ uint4 lds128_generic(const uint8_t* p) {
+  return *reinterpret_cast<const uint4*>(p);
+}
+
+// D[tmem] (+)= A[tmem] . B[smem descriptor]
+__device__ __forceinline__ void mma_f16_ts(uint32_t d_tmem, uint32_t a_tmem, uint64_t b_desc,
+                                           uint32_t idesc, uint32_t accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "setp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, p;\n\t}" ::"r"(d_tmem),
+      "r"(a_tmem), "l"(b_desc), "r"(idesc), "r"(accumulate)
+      : "memory");
+}
+
+// 32 registers of this thread into its lane of tensor memory, columns [taddr, taddr + 32).
+__device__ __forceinline__ void tmem_store_32cols(uint32_t taddr, const uint32_t (&v)[32]) {
+  asm volatile(
+      "tcgen05.st.sync.aligned.32x32b.x32.b32 [%0], "
+      "{%1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, %16, "
+      "%17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31, %32};" ::"r"(taddr),
+      "r"(v[0]), "r"(v[1]), "r"(v[2]), "r"(v[3]), "r"(v[4]), "r"(v[5]), "r"(v[6]), "r"(v[7]), "r"(v[8]),
+      "r"(v[9]), "r"(v[10]), "r"(v[11]), "r"(v[12]), "r"(v[13]), "r"(v[14]), "r"(v[15]), "r"(v[16]),
+      "r"(v[17]), "r"(v[18]), "r"(v[19]), "r"(v[20]), "r"(v[21]), "r"(v[22]), "r"(v[23]), "r"(v[24]),
+      "r"(v[25]), "r"(v[26]), "r"(v[27]), "r"(v[28]), "r"(v[29]), "r"(v[30]), "r"(v[31])
+      : "memory");
+}
+__device__ __forceinline__ void tmem_store_wait() {
+  asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
+}
+
+__device__ __forceinline__ void tma_load_3d_plain(void* smem_dst, const CUtensorMap* map, int c0, int c1,
+                                                  int c2, uint64_t* bar) {
+  asm volatile(
+      "cp.async.bulk.tensor.3d.shared::cluster.global.tile.mbarrier::complete_tx::bytes "
+      "[%0], [%1, {%2, %3, %4}], [%5];" ::"r"(smem_addr(smem_dst)),
+      "l"(map), "r"(c0), "r"(c1), "r"(c2), "r"(smem_addr(bar))
+      : "memory");
+}
+
+__global__ void __launch_bounds__(kThreads, 1)
+    w4a16_gemm_wt_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_constant__ CUtensorMap tmap_w,
+                         const __grid_constant__ CUtensorMap tmap_s, const __grid_constant__ CUtensorMap tmap_z,
+                         const WtParams p) {
+  extern __shared__ uint8_t smem_raw[];
+  // The swizzled X tiles need 1024-byte alignment.
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) &
+                                             ~static_cast<uintptr_t>(1023));
+  const int x_stage_bytes = p.tokens * kBK * 2;
+  uint8_t* smem_x = smem;
+  uint8_t* smem_w = smem_x + p.stages * x_stage_bytes;
+  uint8_t* smem_meta = smem_w + p.stages * kPackedTileBytes;
+  Barriers* bars = reinterpret_cast<Barriers*>(smem_meta + 2 * kMetaSlotBytes);
+  volatile int* abort_flag = &bars->abort_flag;
+
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+  // Grid order: slices of one tile are neighbours; tiles of one row block follow each other, so
+  // that the CTAs of a wave share X blocks and weight rows in the L2.
+  const int slice = blockIdx.x % p.slices;
+  const int tile = blockIdx.x / p.slices;
+  const int n_block = tile / p.m_tiles;
+  const int m_tile = tile - n_block * p.m_tiles;
+  const int n0 = n_block * kRowsW;
+  const int m0 = m_tile * p.tokens;
+  const int sb_total = p.K / 256;
+  const int sb_begin = slice * sb_total / p.slices;
+  const int sb_end = (slice + 1) * sb_total / p.slices;
+  const int kb_begin = sb_begin * 4;
+  const int k_blocks = (sb_end - sb_begin) * 4;
+  const uint32_t idesc = instr_desc_f16(128, static_cast<uint32_t>(p.tokens));
+  const uint32_t a_base_col = static_cast<uint32_t>(2 * p.tokens);  // A slots follow the accumulators
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < p.stages; ++s) {
+      mbar_init(&bars->full[s], 1);
+      mbar_init(&bars->x_empty[s], 1);
+      mbar_init(&bars->w_empty[s], kDequantWarps);
+    }
+    for (int s = 0; s < 2; ++s) {
+      mbar_init(&bars->meta_full[s], 1);
+      mbar_init(&bars->meta_empty[s], kDequantWarps);
+    }
+    for (int s = 0; s < p.a_slots; ++s) {
+      mbar_init(&bars->a_full[s], kDequantWarps);
+      mbar_init(&bars->a_empty[s], 1);
+    }
+    mbar_init(&bars->acc_full, 1);
+    bars->abort_flag = 0;
+    mbar_init_fence();
+  }
+  if (warp == 1) {
+    tmem_alloc(&bars->tmem_base, kTmemCols);
+    tmem_relinquish();
+  }
+  tc_fence_before_sync();
+  __syncthreads();
+  tc_fence_after_sync();
+  const uint32_t tmem_base = *reinterpret_cast<volatile uint32_t*>(&bars->tmem_base);
+  pdl_allow_next_kernel();
+
+  if (warp == 0) {
+    // ------------------------------- copy producer ---------------------------------------------
+    if (lane == 0) {
+      pdl_wait_for_previous_kernel();
+      for (int kb = 0; kb < k_blocks; ++kb) {
+        if ((kb & 3) == 0) {
+          const int sb = kb >> 2;
+          const int ms = sb & 1;
+          const int mround = sb >> 1;
+          if (mround > 0) {
+            mbar_wait_bounded(&bars->meta_empty[ms], (mround - 1) & 1, abort_flag, p.status, kStatusWtWait + 1);
+          }
+          if (*abort_flag) break;
+          uint8_t* dst = smem_meta + ms * kMetaSlotBytes;
+          mbar_arrive_expect_tx(&bars->meta_full[ms], kMetaSlotBytes);
+          tma_load_2d(dst, &tmap_s, kb_begin + kb, n0, &bars->meta_full[ms]);
+          tma_load_2d(dst + kMetaTileBytes, &tmap_z, kb_begin + kb, n0, &bars->meta_full[ms]);
+        }
+        const int s = kb % p.stages;
+        const int round = kb / p.stages;
+        if (round > 0) {
+          mbar_wait_bounded(&bars->x_empty[s], (round - 1) & 1, abort_flag, p.status, kStatusWtWait + 2);
+          mbar_wait_bounded(&bars->w_empty[s], (round - 1) & 1, abort_flag, p.status, kStatusWtWait + 3);
+        }
+        if (*abort_flag) break;
+        mbar_arrive_expect_tx(&bars->full[s], static_cast<uint32_t>(x_stage_bytes + kPackedTileBytes));
+        tma_load_2d(smem_x + s * x_stage_bytes, &tmap_x, (kb_begin + kb) * kBK, m0, &bars->full[s]);
+        tma_load_3d_plain(smem_w + s * kPackedTileBytes, &tmap_w, 0, kb_begin + kb, n0, &bars->full[s]);
+      }
+    }
+  } else if (warp == 1) {
+    // ------------------------------- MMA issuer ------------------------------------------------
+    if (lane == 0) {
+      for (int kb = 0; kb < k_blocks; ++kb) {
+        const int s = kb % p.stages;
+        const int round = kb / p.stages;
+        const int slot = kb % p.a_slots;
+        const int around = kb / p.a_slots;
+        mbar_wait_bounded(&bars->full[s], round & 1, abort_flag, p.status, kStatusWtWait + 4);
+        mbar_wait_bounded(&bars->a_full[slot], around & 1, abort_flag, p.status, kStatusWtWait + 5);
+        if (*abort_flag) break;
+        tc_fence_after_sync();
+        const uint32_t x_addr = smem_addr(smem_x + s * x_stage_bytes);
+#pragma unroll
+        for (int kk = 0; kk < kBK / 16; ++kk) {
+          const uint64_t b_desc = smem_desc_k_major_sw128(x_addr + kk * 32);
+#pragma unroll
+          for (int b = 0; b < 2; ++b) {
+            const uint32_t a_col = a_base_col + static_cast<uint32_t>((slot * 2 + b) * 32 + kk * 8);
+            mma_f16_ts(tmem_base + static_cast<uint32_t>(b * p.tokens), tmem_base + a_col, b_desc, idesc,
+                       (kb | kk) != 0 ? 1u : 0u);
+          }
+        }
+        mma_commit(&bars->x_empty[s]);
+        mma_commit(&bars->a_empty[slot]);
+      }
+      if (!*abort_flag) mma_commit(&bars->acc_full);
+    }
+  } else {
+    // ------------------------------- dequantisation warps --------------------------------------
+    const int quarter = warp & 3;          // TMEM lanes this warp may touch: 32 * quarter ..
+    const int block = (warp - 2) >> 2;     // MMA block (accumulator) of this warp
+    const int row = block * 128 + quarter * 32 + lane;  // weight row within the CTA's 256
+    const uint32_t lane_base = static_cast<uint32_t>(quarter * 32) << 16;
+    for (int sb = 0; sb * 4 < k_blocks; ++sb) {
+      const int ms = sb & 1;
+      const int mround = sb >> 1;
+      mbar_wait_bounded(&bars->meta_full[ms], mround & 1, abort_flag, p.status, kStatusWtWait + 6);
+      const uint8_t* meta = smem_meta + ms * kMetaSlotBytes + row * 16;
+      const uint4 scale_bits = lds128_generic(meta);
+      const uint4 zero_bits = lds128_generic(meta + kMetaTileBytes);
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&bars->meta_empty[ms]);
+      const float sc[4] = {__uint_as_float(scale_bits.x), __uint_as_float(scale_bits.y),
+                           __uint_as_float(scale_bits.z), __uint_as_float(scale_bits.w)};
+      const int zp[4] = {static_cast<int>(zero_bits.x), static_cast<int>(zero_bits.y),
+                         static_cast<int>(zero_bits.z), static_cast<int>(zero_bits.w)};
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        const int kb = sb * 4 + j;
+        const int s = kb % p.stages;
+        const int round = kb / p.stages;
+        mbar_wait_bounded(&bars->full[s], round & 1, abort_flag, p.status, kStatusWtWait + 7);
+        const uint8_t* words = smem_w + s * kPackedTileBytes + row * kPackedPitch;
+        const uint4 w0 = lds128_generic(words);
+        const uint4 w1 = lds128_generic(words + 16);
+        __syncwarp();
+        if (lane == 0) mbar_arrive(&bars->w_empty[s]);
+        const int slot = kb % p.a_slots;
+        const int around = kb / p.a_slots;
+        if (around > 0) {
+          mbar_wait_bounded(&bars->a_empty[slot], (around - 1) & 1, abort_flag, p.status, kStatusWtWait + 8);
+          tc_fence_after_sync();
+        }
+        const GroupConstants group = group_constants(sc[j], zp[j]);
+        const uint32_t w[8] = {w0.x, w0.y, w0.z, w0.w, w1.x, w1.y, w1.z, w1.w};
+        uint32_t v[32];
+#pragma unroll
+        for (int c = 0; c < 8; ++c) {
+          const uint4 out = dequant_word(w[c], group);
+          v[4 * c + 0] = out.x, v[4 * c + 1] = out.y, v[4 * c + 2] = out.z, v[4 * c + 3] = out.w;
+        }
+        tmem_store_32cols(tmem_base + lane_base + a_base_col + static_cast<uint32_t>((slot * 2 + block) * 32), v);
+        tmem_store_wait();
+        tc_fence_before_sync();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(&bars->a_full[slot]);
+      }
+    }
+
+    // ------------------------------- epilogue ---------------------------------------------------
+    const bool ok = mbar_wait_bounded(&bars->acc_full, 0, abort_flag, p.status, kStatusWtWait + 9);
+    tc_fence_after_sync();
+    pdl_wait_for_previous_kernel();  // before the first write to Y or the scratch
+    const int r = block * 128 + quarter * 32 + lane;  // weight row of the tile
+    const uint32_t taddr = tmem_base + lane_base + static_cast<uint32_t>(block * p.tokens);
+    const int tokens_here = min(p.tokens, p.M - m0);
+    const bool row_ok = n0 + r < p.N;
+    if (p.slices == 1) {
+      if (ok) {
+        __half* out = p.y + static_cast<size_t>(m0) * p.N + n0 + r;
+        for (int c0 = 0; c0 < tokens_here; c0 += 32) {
+          // A chunk may reach past BT into the columns that follow; those values belong to tokens
+          // that do not exist and are never stored.
+          uint32_t v[32];
+          tmem_load_32cols(taddr + c0, v);
+          tmem_load_wait();
+          if (row_ok) {
+#pragma unroll
+            for (int i = 0; i < 32; ++i) {
+              if (c0 + i < tokens_here) out[static_cast<size_t>(c0 + i) * p.N] = __float2half_rn(__uint_as_float(v[i]));
+            }
+          }
+        }
+      }
+    } else {
+      // One slice of K: FP32 partial tile [token][weight row] to the scratch, then the ticket.
+      float* block_partials = p.partials + static_cast<size_t>(n_block) * p.slices * p.M * kRowsW;
+      if (ok) {
+        float* dst = block_partials + static_cast<size_t>(slice) * p.M * kRowsW + r;
+        for (int c0 = 0; c0 < tokens_here; c0 += 32) {
+          uint32_t v[32];
+          tmem_load_32cols(taddr + c0, v);
+          tmem_load_wait();
+#pragma unroll
+          for (int i = 0; i < 32; ++i) {
+            if (c0 + i < tokens_here) dst[static_cast<size_t>(c0 + i) * kRowsW] = __uint_as_float(v[i]);
+          }
+        }
+      }
+      __threadfence();
+      named_barrier(1, kDequantWarps * 32);
+      if (threadIdx.x == 64) bars->ticket = atomicAdd(&p.tickets[n_block], 1);
+      named_barrier(1, kDequantWarps * 32);
+      if (bars->ticket == p.slices - 1) {
+        __threadfence();
+        // Last slice of this row block to arrive: add the partial tiles in slice order.  A warp
+        // takes one token at a time, a lane eight neighbouring weight rows (two 16-byte loads per
+        // slice, all slices in flight together).
+        const int oct = lane * 8;
+        for (int t = warp - 2; t < p.M; t += kDequantWarps) {
+          float4 part[kMaxSlices][2];
+#pragma unroll
+          for (int s = 0; s < kMaxSlices; ++s) {
+            if (s < p.slices) {
+              const float* src = block_partials + (static_cast<size_t>(s) * p.M + t) * kRowsW + oct;
+              part[s][0] = __ldcg(reinterpret_cast<const float4*>(src));
+              part[s][1] = __ldcg(reinterpret_cast<const float4*>(src + 4));
+            }
+          }
+          float4 lo = make_float4(0.0f, 0.0f, 0.0f, 0.0f), hi = lo;
+#pragma unroll
+          for (int s = 0; s < kMaxSlices; ++s) {
+            if (s < p.slices) {
+              lo.x += part[s][0].x, lo.y += part[s][0].y, lo.z += part[s][0].z, lo.w += part[s][0].w;
+              hi.x += part[s][1].x, hi.y += part[s][1].y, hi.z += part[s][1].z, hi.w += part[s][1].w;
+            }
+          }
+          if (n0 + oct < p.N) {
+            const __half2 h0 = __floats2half2_rn(lo.x, lo.y), h1 = __floats2half2_rn(lo.z, lo.w);
+            const __half2 h2 = __floats2half2_rn(hi.x, hi.y), h3 = __floats2half2_rn(hi.z, hi.w);
+            uint4 o;
+            o.x = *reinterpret_cast<const uint32_t*>(&h0);
+            o.y = *reinterpret_cast<const uint32_t*>(&h1);
+            o.z = *reinterpret_cast<const uint32_t*>(&h2);
+            o.w = *reinterpret_cast<const uint32_t*>(&h3);
+            *reinterpret_cast<uint4*>(p.y + static_cast<size_t>(t) * p.N + n0 + oct) = o;
+          }
+        }
+        if (threadIdx.x == 64) p.tickets[n_block] = 0;
+      }
+    }
+  }
+
+  if (*abort_flag) {
+    // Give copies that are still in flight time to land before the shared memory is released.
+    const long long start = clock64();
+    while (clock64() - start < 200000) {
+    }
+  }
+  tc_fence_before_sync();
+  __syncthreads();
+  if (warp == 1) {
+    tc_fence_after_sync();
+    tmem_dealloc(tmem_base, kTmemCols);
+  }
+}
+
+struct WtPlan {
+  int tokens, m_tiles, slices, stages, a_slots, smem_bytes;
+};
+
+// Tokens per CTA: the fewest tiles of at most 192 tokens, evenly sized, rounded up to 16.
+// Slices of K only when there is a single token tile: among 1..8 (at least two super blocks each)
+// the smallest count whose last wave of sm_count CTAs is at least 90 % full, else the fullest.
+WtPlan make_plan(int64_t M, int64_t N, int64_t K, int sm_count, bool allow_slices) {
+  WtPlan plan;
+  const int64_t tiles = (M + kMaxTokens - 1) / kMaxTokens;
+  plan.m_tiles = static_cast<int>(tiles);
+  plan.tokens = static_cast<int>(((M + tiles - 1) / tiles + 15) / 16 * 16);
+  plan.m_tiles = static_cast<int>((M + plan.tokens - 1) / plan.tokens);
+  plan.slices = 1;
+  const int64_t n_blocks = (N + kRowsW - 1) / kRowsW;
+  if (plan.m_tiles == 1 && allow_slices) {
+    int64_t most = K / 256 / 2;
+    if (most > kMaxSlices) most = kMaxSlices;
+    if (most < 1) most = 1;
+    const int64_t wave = sm_count > 0 ? sm_count : 148;
+    int best = 1;
+    double best_fill = 0.0;
+    for (int64_t s = 1; s <= most; ++s) {
+      const int64_t ctas = n_blocks * s;
+      const int64_t waves = (ctas + wave - 1) / wave;
+      const double fill = static_cast<double>(ctas) / static_cast<double>(waves * wave);
+      if (fill >= 0.9) {
+        best = static_cast<int>(s);
+        break;
+      }
+      if (fill > best_fill) best_fill = fill, best = static_cast<int>(s);
+    }
+    plan.slices = best;
+  }
+  plan.a_slots = (kTmemCols - 2 * plan.tokens) / 64;
+  if (plan.a_slots > kMaxASlots) plan.a_slots = kMaxASlots;
+  const int stage_bytes = plan.tokens * kBK * 2 + kPackedTileBytes;
+  int stages = (kSmemBudget - 2 * kMetaSlotBytes - kBarrierBytes - 1024) / stage_bytes;
+  if (stages > kMaxStages) stages = kMaxStages;
+  plan.stages = stages;
+  plan.smem_bytes = stages * stage_bytes + 2 * kMetaSlotBytes + kBarrierBytes + 1024;
+  return plan;
+}
+
+}  // namespace
+
+bool gemm_wt_supports(int64_t M, int64_t N, int64_t K) {
+  return M >= 1 && N >= 128 && N % 128 == 0 && K >= 256 && K % 256 == 0 && M <= (1 << 24) &&
+         N <= (1 << 24) && K <= (1 << 24) &&
+         ((N + kRowsW - 1) / kRowsW) * ((M + 15) / 16) <= 0x7fffffffLL / kMaxSlices;
+}
+
+size_t gemm_wt_workspace_bytes(int64_t M, int64_t N, int64_t K, int sm_count) {
+  if (!gemm_wt_supports(M, N, K)) return 0;
+  const WtPlan plan = make_plan(M, N, K, sm_count, true);
+  const int64_t n_blocks = (N + kRowsW - 1) / kRowsW;
+  if (plan.slices == 1 || n_blocks > static_cast<int64_t>(kSkinnyTicketBytes / sizeof(int))) return 0;
+  return kSkinnyTicketBytes + static_cast<size_t>(n_blocks) * plan.slices * M * kRowsW * sizeof(float);
+}
+
+cudaError_t launch_gemm_wt(const Problem& p, int* status_word, cudaStream_t stream, void* workspace,
+                           size_t workspace_bytes, int sm_count, bool pdl) {
+  const size_t need = gemm_wt_workspace_bytes(p.M, p.N, p.K, sm_count);
+  const bool sliced = need > 0 && workspace != nullptr && workspace_bytes >= need;
+  const WtPlan plan = make_plan(p.M, p.N, p.K, sm_count, sliced);
+  CUtensorMap tmap_x, tmap_w, tmap_s, tmap_z;
+  {
+    const uint64_t dims[2] = {static_cast<uint64_t>(p.K), static_cast<uint64_t>(p.M)};
+    const uint64_t strides[1] = {static_cast<uint64_t>(p.K) * sizeof(__half)};
+    const uint32_t box[2] = {kBK, static_cast<uint32_t>(plan.tokens)};
+    if (!encode_tensor_map(&tmap_x, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, p.x, dims, strides, box,
+                           CU_TENSOR_MAP_SWIZZLE_128B)) {
+      return cudaErrorInvalidValue;
+    }
+  }
+  {
+    // Packed words as [N][K / 64][4 x 8 bytes]; the box takes six 8-byte elements per row, two of
+    // them outside the inner extent (zero-filled): a 48-byte pitch in shared memory.
+    const uint64_t dims[3] = {4, static_cast<uint64_t>(p.K / 64), static_cast<uint64_t>(p.N)};
+    const uint64_t strides[2] = {32, static_cast<uint64_t>(p.K / 2)};
+    const uint32_t box[3] = {kPackedPitch / 8, 1, kRowsW};
+    if (!encode_tensor_map(&tmap_w, CU_TENSOR_MAP_DATA_TYPE_UINT64, 3, p.packed, dims, strides, box,
+                           CU_TENSOR_MAP_SWIZZLE_NONE)) {
+      return cudaErrorInvalidValue;
+    }
+  }
+  {
+    const uint64_t dims[2] = {static_cast<uint64_t>(p.K / 64), static_cast<uint64_t>(p.N)};
+    const uint64_t strides[1] = {static_cast<uint64_t>(p.K / 64) * 4};
+    const uint32_t box[2] = {4, kRowsW};
+    if (!encode_tensor_map(&tmap_s, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 2, p.scales, dims, strides, box,
+                           CU_TENSOR_MAP_SWIZZLE_NONE) ||
+        !encode_tensor_map(&tmap_z, CU_TENSOR_MAP_DATA_TYPE_INT32, 2, p.zeros, dims, strides, box,
+                           CU_TENSOR_MAP_SWIZZLE_NONE)) {
+      return cudaErrorInvalidValue;
+    }
+  }
+
+  static bool configured[64] = {};
+  int device = 0;
+  cudaError_t err = cudaGetDevice(&device);
+  if (err != cudaSuccess) return err;
+  if (device < 0 || device >= 64 || !configured[device]) {
+    err = cudaFuncSetAttribute(w4a16_gemm_wt_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBudget);
+    if (err != cudaSuccess) return err;
+    if (device >= 0 && device < 64) configured[device] = true;
+  }
+
+  WtParams wp;
+  wp.y = p.y;
+  wp.M = static_cast<int>(p.M);
+  wp.N = static_cast<int>(p.N);
+  wp.K = static_cast<int>(p.K);
+  wp.tokens = plan.tokens;
+  wp.m_tiles = plan.m_tiles;
+  wp.slices = plan.slices;
+  wp.stages = plan.stages;
+  wp.a_slots = plan.a_slots;
+  wp.partials = nullptr;
+  wp.tickets = nullptr;
+  wp.status = status_word;
+  if (plan.slices > 1) {
+    wp.tickets = static_cast<int*>(workspace);
+    wp.partials = reinterpret_cast<float*>(static_cast<char*>(workspace) + kSkinnyTicketBytes);
+  }
+  const int64_t n_blocks = (p.N + kRowsW - 1) / kRowsW;
+  const unsigned grid = static_cast<unsigned>(n_blocks * plan.m_tiles * plan.slices);
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3(grid);
+  cfg.blockDim = dim3(kThreads);
+  cfg.dynamicSmemBytes = static_cast<size_t>(plan.smem_bytes);
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = pdl ? 1 : 0;
+  return cudaLaunchKernelEx(&cfg, w4a16_gemm_wt_kernel, tmap_x, tmap_w, tmap_s, tmap_z, wp);
+}
+
+}  // namespace lbl

@@ -135,4 +135,12 @@ size_t gemm_tc_small_workspace_bytes(int64_t M, int64_t N, int64_t K, int sm_cou
 cudaError_t launch_gemm_tc_small(const Problem& p, int* status_word, cudaStream_t stream, void* workspace,
                                  size_t workspace_bytes, int sm_count, bool pdl);
 
+
+// ----- tcgen05 GEMM with the weights passed through tensor memory (gemm_wt.cu) ------------------
+bool gemm_wt_supports(int64_t M, int64_t N, int64_t K);
+// Scratch that lets K be cut into slices when there are few tokens and few row blocks (0: none).
+size_t gemm_wt_workspace_bytes(int64_t M, int64_t N, int64_t K, int sm_count);
+cudaError_t launch_gemm_wt(const Problem& p, int* status_word, cudaStream_t stream, void* workspace,
+                           size_t workspace_bytes, int sm_count, bool pdl);
+
 }  // namespace lbl
