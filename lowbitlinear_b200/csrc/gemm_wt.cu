@@ -42,12 +42,26 @@
 namespace lbl {
 namespace {
 
+#ifdef LBL_WT_SPIN
+#define WT_WAIT mbar_spin_bounded
+#else
+#define WT_WAIT mbar_wait_bounded
+#endif
+
 constexpr int kRowsW = 256;     // weight rows per CTA: two MMA blocks of 128
 constexpr int kBK = 64;
-constexpr int kMaxTokens = 192;
+#ifndef LBL_WT_TOKENS
+#define LBL_WT_TOKENS 192
+#endif
+constexpr int kMaxTokens = LBL_WT_TOKENS;
 constexpr int kMaxStages = 8;
 constexpr int kMaxASlots = 4;
-constexpr int kDequantWarps = 8;
+#ifndef LBL_WT_WARPS
+#define LBL_WT_WARPS 16
+#endif
+constexpr int kDequantWarps = LBL_WT_WARPS;   // 8: one thread per weight row; 16: two, half a k-block each
+constexpr int kThreadsPerRow = kDequantWarps / 8;
+constexpr int kWordsPerThread = 8 / kThreadsPerRow;
 constexpr int kThreads = 32 * (2 + kDequantWarps);
 constexpr int kTmemCols = 512;
 constexpr int kPackedPitch = 48;                     // bytes per row of a packed tile in shared memory
@@ -103,7 +117,7 @@ __device__ __forceinline__ void mma_f16_ts(uint32_t d_tmem, uint32_t a_tmem, uin
 }
 
 // 32 registers of this thread into its lane of tensor memory, columns [taddr, taddr + 32).
-__device__ __forceinline__ void tmem_store_32cols(uint32_t taddr, const uint32_t (&v)[32]) {
+__device__ __forceinline__ void tmem_store_cols(uint32_t taddr, const uint32_t (&v)[32]) {
   asm volatile(
       "tcgen05.st.sync.aligned.32x32b.x32.b32 [%0], "
       "{%1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, %16, "
@@ -112,6 +126,14 @@ __device__ __forceinline__ void tmem_store_32cols(uint32_t taddr, const uint32_t
       "r"(v[9]), "r"(v[10]), "r"(v[11]), "r"(v[12]), "r"(v[13]), "r"(v[14]), "r"(v[15]), "r"(v[16]),
       "r"(v[17]), "r"(v[18]), "r"(v[19]), "r"(v[20]), "r"(v[21]), "r"(v[22]), "r"(v[23]), "r"(v[24]),
       "r"(v[25]), "r"(v[26]), "r"(v[27]), "r"(v[28]), "r"(v[29]), "r"(v[30]), "r"(v[31])
+      : "memory");
+}
+__device__ __forceinline__ void tmem_store_cols(uint32_t taddr, const uint32_t (&v)[16]) {
+  asm volatile(
+      "tcgen05.st.sync.aligned.32x32b.x16.b32 [%0], "
+      "{%1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, %16};" ::"r"(taddr),
+      "r"(v[0]), "r"(v[1]), "r"(v[2]), "r"(v[3]), "r"(v[4]), "r"(v[5]), "r"(v[6]), "r"(v[7]), "r"(v[8]),
+      "r"(v[9]), "r"(v[10]), "r"(v[11]), "r"(v[12]), "r"(v[13]), "r"(v[14]), "r"(v[15])
       : "memory");
 }
 __device__ __forceinline__ void tmem_store_wait() {
@@ -202,9 +224,13 @@ __global__ void __launch_bounds__(kThreads, 1)
           }
           if (*abort_flag) break;
           uint8_t* dst = smem_meta + ms * kMetaSlotBytes;
+#ifdef LBL_WT_SKIP_TMA
+          mbar_arrive(&bars->meta_full[ms]);
+#else
           mbar_arrive_expect_tx(&bars->meta_full[ms], kMetaSlotBytes);
           tma_load_2d(dst, &tmap_s, kb_begin + kb, n0, &bars->meta_full[ms]);
           tma_load_2d(dst + kMetaTileBytes, &tmap_z, kb_begin + kb, n0, &bars->meta_full[ms]);
+#endif
         }
         const int s = kb % p.stages;
         const int round = kb / p.stages;
@@ -213,9 +239,13 @@ __global__ void __launch_bounds__(kThreads, 1)
           mbar_wait_bounded(&bars->w_empty[s], (round - 1) & 1, abort_flag, p.status, kStatusWtWait + 3);
         }
         if (*abort_flag) break;
+#ifdef LBL_WT_SKIP_TMA
+        mbar_arrive(&bars->full[s]);
+#else
         mbar_arrive_expect_tx(&bars->full[s], static_cast<uint32_t>(x_stage_bytes + kPackedTileBytes));
         tma_load_2d(smem_x + s * x_stage_bytes, &tmap_x, (kb_begin + kb) * kBK, m0, &bars->full[s]);
         tma_load_3d_plain(smem_w + s * kPackedTileBytes, &tmap_w, 0, kb_begin + kb, n0, &bars->full[s]);
+#endif
       }
     }
   } else if (warp == 1) {
@@ -226,8 +256,8 @@ __global__ void __launch_bounds__(kThreads, 1)
         const int round = kb / p.stages;
         const int slot = kb % p.a_slots;
         const int around = kb / p.a_slots;
-        mbar_wait_bounded(&bars->full[s], round & 1, abort_flag, p.status, kStatusWtWait + 4);
-        mbar_wait_bounded(&bars->a_full[slot], around & 1, abort_flag, p.status, kStatusWtWait + 5);
+        WT_WAIT(&bars->full[s], round & 1, abort_flag, p.status, kStatusWtWait + 4);
+        WT_WAIT(&bars->a_full[slot], around & 1, abort_flag, p.status, kStatusWtWait + 5);
         if (*abort_flag) break;
         tc_fence_after_sync();
         const uint32_t x_addr = smem_addr(smem_x + s * x_stage_bytes);
@@ -237,8 +267,13 @@ __global__ void __launch_bounds__(kThreads, 1)
 #pragma unroll
           for (int b = 0; b < 2; ++b) {
             const uint32_t a_col = a_base_col + static_cast<uint32_t>((slot * 2 + b) * 32 + kk * 8);
+#if defined(LBL_WT_SS_MMA)
+            mma_f16(tmem_base + static_cast<uint32_t>(b * p.tokens), smem_desc_k_major_sw128(x_addr + kk * 32), b_desc,
+                    idesc, (kb | kk) != 0 ? 1u : 0u);
+#elif !defined(LBL_WT_SKIP_MMA)
             mma_f16_ts(tmem_base + static_cast<uint32_t>(b * p.tokens), tmem_base + a_col, b_desc, idesc,
                        (kb | kk) != 0 ? 1u : 0u);
+#endif
           }
         }
         mma_commit(&bars->x_empty[s]);
@@ -248,14 +283,15 @@ __global__ void __launch_bounds__(kThreads, 1)
     }
   } else {
     // ------------------------------- dequantisation warps --------------------------------------
-    const int quarter = warp & 3;          // TMEM lanes this warp may touch: 32 * quarter ..
-    const int block = (warp - 2) >> 2;     // MMA block (accumulator) of this warp
+    const int quarter = warp & 3;                // TMEM lanes this warp may touch: 32 * quarter ..
+    const int block = ((warp - 2) >> 2) & 1;     // MMA block (accumulator) of this warp
+    const int part = (warp - 2) >> 3;            // which piece of the k-block's 64 columns (two threads per row)
     const int row = block * 128 + quarter * 32 + lane;  // weight row within the CTA's 256
     const uint32_t lane_base = static_cast<uint32_t>(quarter * 32) << 16;
     for (int sb = 0; sb * 4 < k_blocks; ++sb) {
       const int ms = sb & 1;
       const int mround = sb >> 1;
-      mbar_wait_bounded(&bars->meta_full[ms], mround & 1, abort_flag, p.status, kStatusWtWait + 6);
+      WT_WAIT(&bars->meta_full[ms], mround & 1, abort_flag, p.status, kStatusWtWait + 6);
       const uint8_t* meta = smem_meta + ms * kMetaSlotBytes + row * 16;
       const uint4 scale_bits = lds128_generic(meta);
       const uint4 zero_bits = lds128_generic(meta + kMetaTileBytes);
@@ -270,27 +306,46 @@ __global__ void __launch_bounds__(kThreads, 1)
         const int kb = sb * 4 + j;
         const int s = kb % p.stages;
         const int round = kb / p.stages;
-        mbar_wait_bounded(&bars->full[s], round & 1, abort_flag, p.status, kStatusWtWait + 7);
-        const uint8_t* words = smem_w + s * kPackedTileBytes + row * kPackedPitch;
-        const uint4 w0 = lds128_generic(words);
-        const uint4 w1 = lds128_generic(words + 16);
+        WT_WAIT(&bars->full[s], round & 1, abort_flag, p.status, kStatusWtWait + 7);
+        const uint8_t* words = smem_w + s * kPackedTileBytes + row * kPackedPitch + part * 16;
+        uint32_t w[kWordsPerThread];
+        {
+          const uint4 w0 = lds128_generic(words);
+          w[0] = w0.x, w[1] = w0.y, w[2] = w0.z, w[3] = w0.w;
+          if (kWordsPerThread == 8) {
+            const uint4 w1 = lds128_generic(words + 16);
+            w[kWordsPerThread - 4] = w1.x, w[kWordsPerThread - 3] = w1.y;
+            w[kWordsPerThread - 2] = w1.z, w[kWordsPerThread - 1] = w1.w;
+          }
+        }
         __syncwarp();
         if (lane == 0) mbar_arrive(&bars->w_empty[s]);
         const int slot = kb % p.a_slots;
         const int around = kb / p.a_slots;
         if (around > 0) {
-          mbar_wait_bounded(&bars->a_empty[slot], (around - 1) & 1, abort_flag, p.status, kStatusWtWait + 8);
+          WT_WAIT(&bars->a_empty[slot], (around - 1) & 1, abort_flag, p.status, kStatusWtWait + 8);
           tc_fence_after_sync();
         }
+#ifdef LBL_WT_SKIP_DEQUANT
+        tc_fence_before_sync();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(&bars->a_full[slot]);
+        continue;
+#endif
         const GroupConstants group = group_constants(sc[j], zp[j]);
-        const uint32_t w[8] = {w0.x, w0.y, w0.z, w0.w, w1.x, w1.y, w1.z, w1.w};
-        uint32_t v[32];
+        uint32_t v[4 * kWordsPerThread];
 #pragma unroll
-        for (int c = 0; c < 8; ++c) {
+        for (int c = 0; c < kWordsPerThread; ++c) {
+#ifdef LBL_WT_NO_ARITHMETIC
+          v[4 * c + 0] = w[c], v[4 * c + 1] = w[c] >> 4, v[4 * c + 2] = w[c] >> 8, v[4 * c + 3] = __float_as_uint(group.s01.x);
+#else
           const uint4 out = dequant_word(w[c], group);
           v[4 * c + 0] = out.x, v[4 * c + 1] = out.y, v[4 * c + 2] = out.z, v[4 * c + 3] = out.w;
+#endif
         }
-        tmem_store_32cols(tmem_base + lane_base + a_base_col + static_cast<uint32_t>((slot * 2 + block) * 32), v);
+        const uint32_t a_addr = tmem_base + lane_base + a_base_col +
+                                static_cast<uint32_t>((slot * 2 + block) * 32 + part * 4 * kWordsPerThread);
+        tmem_store_cols(a_addr, v);  // 32 or 16 columns, by the array's size
         tmem_store_wait();
         tc_fence_before_sync();
         __syncwarp();
@@ -302,25 +357,31 @@ __global__ void __launch_bounds__(kThreads, 1)
     const bool ok = mbar_wait_bounded(&bars->acc_full, 0, abort_flag, p.status, kStatusWtWait + 9);
     tc_fence_after_sync();
     pdl_wait_for_previous_kernel();  // before the first write to Y or the scratch
-    const int r = block * 128 + quarter * 32 + lane;  // weight row of the tile
+    const int r = row;  // weight row of the tile
     const uint32_t taddr = tmem_base + lane_base + static_cast<uint32_t>(block * p.tokens);
     const int tokens_here = min(p.tokens, p.M - m0);
     const bool row_ok = n0 + r < p.N;
+    // Warps that share a block and a lane quarter take alternate chunks of 32 tokens.
+    const int chunk_first = 32 * part, chunk_step = 32 * kThreadsPerRow;
     if (p.slices == 1) {
       if (ok) {
         __half* out = p.y + static_cast<size_t>(m0) * p.N + n0 + r;
-        for (int c0 = 0; c0 < tokens_here; c0 += 32) {
+        for (int c0 = chunk_first; c0 < tokens_here; c0 += chunk_step) {
           // A chunk may reach past BT into the columns that follow; those values belong to tokens
           // that do not exist and are never stored.
           uint32_t v[32];
           tmem_load_32cols(taddr + c0, v);
           tmem_load_wait();
+#ifdef LBL_WT_SKIP_EPILOGUE
+          if (row_ok && v[0] == 0x12345678u) out[0] = __float2half_rn(__uint_as_float(v[1]));
+#else
           if (row_ok) {
 #pragma unroll
             for (int i = 0; i < 32; ++i) {
               if (c0 + i < tokens_here) out[static_cast<size_t>(c0 + i) * p.N] = __float2half_rn(__uint_as_float(v[i]));
             }
           }
+#endif
         }
       }
     } else {
@@ -328,7 +389,7 @@ __global__ void __launch_bounds__(kThreads, 1)
       float* block_partials = p.partials + static_cast<size_t>(n_block) * p.slices * p.M * kRowsW;
       if (ok) {
         float* dst = block_partials + static_cast<size_t>(slice) * p.M * kRowsW + r;
-        for (int c0 = 0; c0 < tokens_here; c0 += 32) {
+        for (int c0 = chunk_first; c0 < tokens_here; c0 += chunk_step) {
           uint32_t v[32];
           tmem_load_32cols(taddr + c0, v);
           tmem_load_wait();
