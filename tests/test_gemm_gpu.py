@@ -138,6 +138,44 @@ def test_small_m_tensor_core_path_against_oracle(m, n, k, cuda_ops):
     torch.testing.assert_close(y.cpu(), expected, atol=atol, rtol=RTOL)
 
 
+@pytest.mark.parametrize("m,n,k", [(1, 128, 256), (16, 256, 256), (130, 256, 512), (192, 512, 1024), (200, 256, 256),
+                                   (64, 4096, 4096), (500, 768, 2048), (385, 384, 4096), (1024, 1024, 1024)])
+def test_tensor_memory_path_against_oracle(m, n, k, cuda_ops):
+    """tcgen05 GEMM with the weights handed to the MMA through tensor memory: FP16-rounded weights as
+    in the reference GEMM, any M (tiles of up to 192 tokens), N % 128 == 0 with a half-empty last
+    row block, K cut into slices that meet in the scratch when there is one token tile."""
+    from lowbitlinear_b200 import _ops
+
+    x, packed, scales, zeros = seeded_layer(m, n, k, seed=m + n + k, std=1.0, device=cuda_ops)
+    expected = oracle_linear(x, packed, scales, zeros, mma=True)
+    atol = ATOL * (4 if k > 2048 else 1)  # unit-variance weights: an FP16 step of the outputs is up to 8e-3
+    scratch = torch.zeros(max(16, _ops.workspace_bytes(m, n, k, _ops.PATH_GEMM_WT)), dtype=torch.uint8, device=cuda_ops)
+    runs = [_ops.linear_forced(x, packed, scales, zeros, _ops.PATH_GEMM_WT, workspace=scratch) for _ in range(3)]
+    assert all(taken == _ops.PATH_GEMM_WT for _, taken in runs)
+    assert torch.equal(runs[0][0], runs[1][0]) and torch.equal(runs[0][0], runs[2][0])
+    torch.testing.assert_close(runs[0][0].cpu(), expected, atol=atol, rtol=RTOL)
+    unsliced, _ = _ops.linear_forced(x, packed, scales, zeros, _ops.PATH_GEMM_WT,
+                                     workspace=torch.zeros(16, dtype=torch.uint8, device=cuda_ops))
+    torch.testing.assert_close(unsliced.cpu(), expected, atol=atol, rtol=RTOL)
+
+
+def test_fp16_operand_policy_of_the_tensor_memory_kernel(cuda_ops):
+    """One-hot activations pick single weights: the result must equal the FP16-rounded-weight oracle
+    bit for bit (and differ from the FP32-weight one)."""
+    from lowbitlinear_b200 import _ops
+
+    m, n, k = 200, 256, 256
+    x = torch.zeros(m, k, device=cuda_ops, dtype=torch.float16)
+    x[torch.arange(m), torch.arange(m) % k] = 1.0
+    q = torch.randint(0, 16, (n, k), device=cuda_ops, dtype=torch.uint8)
+    scales = torch.rand(n, k // 64, device=cuda_ops) * 0.1 + 1.0
+    zeros = torch.randint(0, 16, (n, k // 64), device=cuda_ops, dtype=torch.int32)
+    args = x, pack_int4(q), scales, zeros
+    y, taken = _ops.linear_forced(*args, _ops.PATH_GEMM_WT)
+    assert taken == _ops.PATH_GEMM_WT
+    assert torch.equal(y.cpu(), oracle_linear(*args, mma=True))
+
+
 def test_small_m_tensor_core_path_rejects_other_shapes(cuda_ops):
     from lowbitlinear_b200 import _ops
 
