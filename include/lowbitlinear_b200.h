@@ -53,9 +53,11 @@ extern "C" {
 #define LBL_FLAG_PDL 1u            /* programmatic dependent launch: weights are prefetched
                                       before the previous kernel in the stream has finished.
                                       Only set it when that kernel does not write the weights. */
-#define LBL_FLAG_ROUND_WEIGHTS 2u  /* generic kernel: round each dequantised weight to FP16
-                                      before the multiply (the reference GEMM's operand policy,
-                                      csrc/cute_w4a16_gemm.cu:160-162)                        */
+#define LBL_FLAG_ROUND_WEIGHTS 2u  /* round each dequantised weight to FP16 before the multiply (the
+                                      reference GEMM's operand policy, csrc/cute_w4a16_gemm.cu:160-162)
+                                      also where the dispatcher would pick a streaming kernel, which
+                                      keeps the FP32 scale: the any-shape operator then runs a
+                                      tensor-core or the masked kernel instead (slower for M <= 8)  */
 
 /* Library version: major * 10000 + minor * 100 + patch. */
 int lbl_version(void);

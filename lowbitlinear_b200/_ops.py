@@ -122,6 +122,17 @@ def set_programmatic_dependent_launch(enabled):
     _flags = (_flags | FLAG_PDL) if enabled else (_flags & ~FLAG_PDL)
 
 
+def set_reference_gemm_policy(enabled):
+    """Make the any-shape operator round every dequantised weight to FP16 before the product on
+    ALL shapes, as the reference GEMM does (``csrc/cute_w4a16_gemm.cu:160-162``).  By default the
+    shapes it hands to the streaming kernels (M <= 8, or M <= 32 with a ragged N; K % 256 == 0)
+    keep the FP32 scale, which is closer to the FP32 reference path but differs from the
+    reference GEMM's own outputs by up to an FP16 step; with this switch those shapes run a
+    tensor-core or the masked kernel instead (slower)."""
+    global _flags
+    _flags = (_flags | FLAG_ROUND_WEIGHTS) if enabled else (_flags & ~FLAG_ROUND_WEIGHTS)
+
+
 def _raw_stream(device):
     """Handle of the current stream of ``device`` (what ``torch.cuda.current_stream(device)
     .cuda_stream`` returns, without building the Python stream object)."""

@@ -117,6 +117,13 @@ int select_path(int64_t M, int64_t N, int64_t K, int op, int sm_count) {
   if (M >= kTcSmallMinM && lbl::gemm_tc_small_supports(M, N, K) && (!wide || M <= 32 || !tc_ok)) {
     return LBL_PATH_GEMM_TC_SMALL;
   }
+  // More than 128 rows of activations on a shape whose 256 x 256 tiles would leave most SMs idle
+  // (less than half a wave: small N, a tensor-parallel shard): the tensor-memory GEMM cuts K into
+  // slices until the SMs are busy.  Also the only tensor-core kernel for N % 256 == 128.
+  if (M > 128 && lbl::gemm_wt_supports(M, N, K)) {
+    const int64_t tc_ctas = (N / 256) * ((M + 255) / 256);
+    if (!tc_ok || 2 * tc_ctas <= sm_count) return LBL_PATH_GEMM_WT;
+  }
   if (tc_ok && (M >= kTcMinM || (wide && M >= 9) || !skinny_ok)) return LBL_PATH_GEMM_TC;
   if (skinny_ok) {
     lbl::SkinnyPlan plan;
@@ -169,6 +176,20 @@ int run_linear(const void* X, const int32_t* packed_w, const float* scales, cons
   if (!forced) {
     path = forced_path_from_env();
     if (path == LBL_PATH_AUTO) path = select_path(M, N, K, op, info.sm_count);
+  }
+  // The reference GEMM's operand policy on request: the streaming kernels keep the FP32 scale, so
+  // the any-shape operator is sent to a kernel that rounds each dequantised weight to FP16.
+  if (!forced && op == 1 && (flags & LBL_FLAG_ROUND_WEIGHTS) != 0 &&
+      (path == LBL_PATH_GEMV || path == LBL_PATH_GEMV_SPLITK)) {
+    if (lbl::gemm_tc_small_supports(M, N, K)) {
+      path = LBL_PATH_GEMM_TC_SMALL;
+    } else if (lbl::gemm_wt_supports(M, N, K)) {
+      path = LBL_PATH_GEMM_WT;
+    } else if (lbl::gemm_tc_supports(M, N, K)) {
+      path = LBL_PATH_GEMM_TC;
+    } else {
+      path = LBL_PATH_GENERIC;
+    }
   }
   // The fast kernels use 16-byte vector accesses and bulk copies on every operand.
   const bool all_aligned = aligned16(X) && aligned16(packed_w) && aligned16(scales) &&

@@ -93,11 +93,11 @@ struct WtParams {
   int M, N, K;
   int tokens;    // BT
   int m_tiles;   // ceil(M / BT)
-  int slices;    // pieces of K per tile (1 unless m_tiles == 1)
+  int slices;    // pieces of K per tile
   int stages;    // depth of the shared-memory ring
   int a_slots;   // A slots per block in tensor memory
   float* partials;  // [n_block][slice][M][256] FP32 when slices > 1
-  int* tickets;     // one per row block
+  int* tickets;     // one per tile (row block x token tile)
   int* status;
 };
 
@@ -388,7 +388,7 @@ __global__ void __launch_bounds__(kThreads, 1)
       // One slice of K: FP32 partial tile [token][weight row] to the scratch, then the ticket.
       float* block_partials = p.partials + static_cast<size_t>(n_block) * p.slices * p.M * kRowsW;
       if (ok) {
-        float* dst = block_partials + static_cast<size_t>(slice) * p.M * kRowsW + r;
+        float* dst = block_partials + (static_cast<size_t>(slice) * p.M + m0) * kRowsW + r;
         for (int c0 = chunk_first; c0 < tokens_here; c0 += chunk_step) {
           uint32_t v[32];
           tmem_load_32cols(taddr + c0, v);
@@ -401,7 +401,7 @@ __global__ void __launch_bounds__(kThreads, 1)
       }
       __threadfence();
       named_barrier(1, kDequantWarps * 32);
-      if (threadIdx.x == 64) bars->ticket = atomicAdd(&p.tickets[n_block], 1);
+      if (threadIdx.x == 64) bars->ticket = atomicAdd(&p.tickets[tile], 1);
       named_barrier(1, kDequantWarps * 32);
       if (bars->ticket == p.slices - 1) {
         __threadfence();
@@ -409,7 +409,7 @@ __global__ void __launch_bounds__(kThreads, 1)
         // takes one token at a time, a lane eight neighbouring weight rows (two 16-byte loads per
         // slice, all slices in flight together).
         const int oct = lane * 8;
-        for (int t = warp - 2; t < p.M; t += kDequantWarps) {
+        for (int t = m0 + warp - 2; t < m0 + tokens_here; t += kDequantWarps) {
           float4 part[kMaxSlices][2];
 #pragma unroll
           for (int s = 0; s < kMaxSlices; ++s) {
@@ -438,7 +438,7 @@ __global__ void __launch_bounds__(kThreads, 1)
             *reinterpret_cast<uint4*>(p.y + static_cast<size_t>(t) * p.N + n0 + oct) = o;
           }
         }
-        if (threadIdx.x == 64) p.tickets[n_block] = 0;
+        if (threadIdx.x == 64) p.tickets[tile] = 0;
       }
     }
   }
@@ -462,25 +462,25 @@ struct WtPlan {
 };
 
 // Tokens per CTA: the fewest tiles of at most 192 tokens, evenly sized, rounded up to 16.
-// Slices of K only when there is a single token tile: among 1..8 (at least two super blocks each)
-// the smallest count whose last wave of sm_count CTAs is at least 90 % full, else the fullest.
+// Slices of K when the tiles alone cannot fill the SMs (one CTA per SM): among 1..8 (at least two
+// super blocks each) the smallest count whose last wave is at least 90 % full, else the fullest.
 WtPlan make_plan(int64_t M, int64_t N, int64_t K, int sm_count, bool allow_slices) {
   WtPlan plan;
   const int64_t tiles = (M + kMaxTokens - 1) / kMaxTokens;
-  plan.m_tiles = static_cast<int>(tiles);
   plan.tokens = static_cast<int>(((M + tiles - 1) / tiles + 15) / 16 * 16);
   plan.m_tiles = static_cast<int>((M + plan.tokens - 1) / plan.tokens);
   plan.slices = 1;
   const int64_t n_blocks = (N + kRowsW - 1) / kRowsW;
-  if (plan.m_tiles == 1 && allow_slices) {
+  const int64_t base = n_blocks * plan.m_tiles;
+  const int64_t wave = sm_count > 0 ? sm_count : 148;
+  if (allow_slices && base < wave && base <= static_cast<int64_t>(kSkinnyTicketBytes / sizeof(int))) {
     int64_t most = K / 256 / 2;
     if (most > kMaxSlices) most = kMaxSlices;
     if (most < 1) most = 1;
-    const int64_t wave = sm_count > 0 ? sm_count : 148;
     int best = 1;
     double best_fill = 0.0;
     for (int64_t s = 1; s <= most; ++s) {
-      const int64_t ctas = n_blocks * s;
+      const int64_t ctas = base * s;
       const int64_t waves = (ctas + wave - 1) / wave;
       const double fill = static_cast<double>(ctas) / static_cast<double>(waves * wave);
       if (fill >= 0.9) {
@@ -513,7 +513,7 @@ size_t gemm_wt_workspace_bytes(int64_t M, int64_t N, int64_t K, int sm_count) {
   if (!gemm_wt_supports(M, N, K)) return 0;
   const WtPlan plan = make_plan(M, N, K, sm_count, true);
   const int64_t n_blocks = (N + kRowsW - 1) / kRowsW;
-  if (plan.slices == 1 || n_blocks > static_cast<int64_t>(kSkinnyTicketBytes / sizeof(int))) return 0;
+  if (plan.slices == 1) return 0;
   return kSkinnyTicketBytes + static_cast<size_t>(n_blocks) * plan.slices * M * kRowsW * sizeof(float);
 }
 

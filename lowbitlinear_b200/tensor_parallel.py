@@ -164,6 +164,17 @@ class RowParallelLinear(torch.nn.Module):
                 and shard.in_features % 256 == 0 and shard.out_features <= self.exchange.capacity_n
                 and x.dtype == torch.float16 and x.is_contiguous())
 
+    def check_status(self):
+        """Synchronises this rank's GPU and raises if a bounded device-side wait expired since the
+        last check -- for instance a peer that never reported to the fused all-reduce, whose
+        outputs are then NaN."""
+        from . import _ops
+
+        status = _ops.device_status(self.shard.packed_weight.device)
+        if status != 0:
+            raise RuntimeError(f"device status {status}: a bounded wait inside a kernel expired "
+                               "(110 = a tensor-parallel peer did not report in time)")
+
     def forward(self, x):
         rank, world = _world(self.group)
         if not self.input_is_parallel:

@@ -137,7 +137,13 @@ def test_dispatcher_choices_and_scratch_sizes():
         assert name(128, 4096, 12288) == "gemm_tc_small"   # weights on the M side of the MMA
         assert name(16, 24576, 4096) == "gemm_tc_small"
         assert name(64, 24576, 4096) == "gemm_tc"          # wide N: 256-wide tiles fill the SMs
-        assert name(129, 4096, 12288) == "gemm_tc"
+        # More than 128 rows on a shape whose 256 x 256 tiles would fill under half of the SMs: the
+        # tensor-memory GEMM, which cuts K into slices (also the kernel for N % 256 == 128).
+        assert name(129, 4096, 12288) == "gemm_wt"
+        assert name(512, 4096, 12288) == "gemm_wt"
+        assert name(2048, 512, 4096) == "gemm_wt"           # a tensor-parallel shard of O
+        assert name(2048, 4096, 12288) == "gemm_tc"
+        assert name(300, 384, 512) == "gemm_wt"
         assert name(5, 9, 70) == "generic"
         assert name(1, 129, 64) == "generic"
         assert name(2048, 129, 4096) == "generic"
@@ -151,6 +157,8 @@ def test_dispatcher_choices_and_scratch_sizes():
         # slice of K; 32 row blocks are cut 8 ways, 192 row blocks 3 ways (waves of 2 * 148 CTAs)
         assert ws(16, 4096, 4096, _ops.PATH_AUTO) == 64 * 1024 + 32 * 8 * 16 * 128 * 4
         assert ws(16, 24576, 4096, _ops.PATH_AUTO) == 64 * 1024 + 192 * 3 * 16 * 128 * 4
+        # tensor-memory GEMM: one FP32 partial tile [M, 256] per row block and slice (16 blocks cut 8 ways)
+        assert ws(129, 4096, 12288, _ops.PATH_AUTO) == 64 * 1024 + 16 * 8 * 129 * 256 * 4
     finally:
         for k, v in env_backup.items():
             if v is not None:
