@@ -122,7 +122,9 @@ int select_path(int64_t M, int64_t N, int64_t K, int op, int sm_count) {
   // slices until the SMs are busy.  Also the only tensor-core kernel for N % 256 == 128.
   if (M > 128 && lbl::gemm_wt_supports(M, N, K)) {
     const int64_t tc_ctas = (N / 256) * ((M + 255) / 256);
-    if (!tc_ok || 2 * tc_ctas <= sm_count) return LBL_PATH_GEMM_WT;
+    // Measured (B200): it wins below a third of a wave, and up to half a wave when K is long
+    // enough for eight slices.
+    if (!tc_ok || 3 * tc_ctas <= sm_count || (2 * tc_ctas <= sm_count && K >= 8192)) return LBL_PATH_GEMM_WT;
   }
   if (tc_ok && (M >= kTcMinM || (wide && M >= 9) || !skinny_ok)) return LBL_PATH_GEMM_TC;
   if (skinny_ok) {

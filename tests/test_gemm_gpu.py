@@ -252,7 +252,8 @@ def test_prefill_sweep_ends_meet_the_benchmark_tolerance(name, m, cuda_ops):
     x, packed, scales, zeros = seeded_layer(m, n, k, seed=seed + 10, device=cuda_ops)
     # Down at M = 512 is 32 tiles of 256 x 256 for 148 SMs: the tensor-memory GEMM with K cut into
     # slices takes it; everything else here fills the SMs with the large tiles.
-    few_tiles = 2 * (n // 256) * ((m + 255) // 256) <= 148
+    tiles = (n // 256) * ((m + 255) // 256)
+    few_tiles = 3 * tiles <= 148 or (2 * tiles <= 148 and k >= 8192)
     assert _ops.select_path(m, n, k) == (_ops.PATH_GEMM_WT if few_tiles else _ops.PATH_GEMM_TC)
     layer = QuantizedLinear(packed, scales, zeros, in_features=k)
     y = layer(x)
