@@ -262,6 +262,7 @@ __global__ void __launch_bounds__(kThreads, 2)
 
   int slot = 0, parity = 0;  // ring position, advanced by counting
   int seq = 0;               // units this CTA has computed
+  const int rotation_step = (p.stage_k / 128) & 7;
   int current_ks = -1;
   UnitCursor cur;
   while (cur.next(p)) {
@@ -289,8 +290,12 @@ __global__ void __launch_bounds__(kThreads, 2)
     for (int st = 0; st < p.stages_per_unit; ++st) {
       mbar_wait_bounded(&hdr->full[slot], parity, abort_flag, p.status, kStatusSkinnyFullWait);
 
+      // Stages whose macro tiles are not a multiple of the eight warps (K = 1536: twelve) would
+      // give four warps twice the work: the warps take the tiles in rotation, as a function of the
+      // row tile and the stage alone (the grouped kernel uses the same one: same bits).
+      const int vwarp = (warp - (cur.rt * p.stages_per_unit + st) * rotation_step) & 7;
       consume_stage(ring_addr + static_cast<uint32_t>(slot * p.slot_bytes), p.packed_pitch, p.meta_pitch,
-                    p.stage_k, st, xf_addr, sx_base, warp, g, t, group_parity, feeds_b, xb, acc_a, acc_b);
+                    p.stage_k, st, xf_addr, sx_base, vwarp, g, t, group_parity, feeds_b, xb, acc_a, acc_b);
       __syncwarp();
       if (lane == 0) mbar_arrive(&hdr->empty[slot]);
       if (++slot == p.slots) slot = 0, parity ^= 1;

@@ -196,6 +196,7 @@ __global__ void __launch_bounds__(kThreads, 2) w4a16_gemv_grouped_kernel(const G
   int slot = 0, parity = 0;  // ring position, advanced by counting
   int seq = 0;               // units this CTA has computed
   int current_problem = -1;
+  int rotation_step = 0;  // see the stage loop
   // Geometry of the current problem.
   int stages_per_unit = 0, packed_pitch = 0, meta_pitch = 0, stage_k = 0;
   bool feeds_b = false;
@@ -216,6 +217,7 @@ __global__ void __launch_bounds__(kThreads, 2) w4a16_gemv_grouped_kernel(const G
       packed_pitch = __ldg(&pr->packed_pitch);
       meta_pitch = __ldg(&pr->meta_pitch);
       stage_k = __ldg(&pr->stage_k);
+      rotation_step = (stage_k / 128) & 7;
       build_activation_operand(pr->x, M, K, K, 0, xf, sx, tid);
       named_barrier(1, kConsumerThreads);
       // B operand: column n = g of this lane carries activation row n / 4 for the k-slots of quad
@@ -235,8 +237,15 @@ __global__ void __launch_bounds__(kThreads, 2) w4a16_gemv_grouped_kernel(const G
       float acc_b = 0.0f;  // row n0 + g + 8
       for (int st = 0; st < stages_per_unit; ++st) {
         mbar_wait_bounded(&hdr->full[slot], parity, abort_flag, p.status, kStatusSkinnyFullWait);
+        // A stage whose 128-column macro tiles are not a multiple of the eight warps (K = 1536 or
+        // 3072: twelve) would give four warps twice the work of the others; the warps take the
+        // tiles in rotation from stage to stage instead, so the leftover moves round.  The warps run
+        // asynchronously (the reducer collects their parts), so balance over a few stages is enough.
+        // The rotation is a function of the row tile and the stage alone, so that every kernel
+        // that computes this unit adds its parts in the same order (same bits).
+        const int vwarp = (warp - (rt * stages_per_unit + st) * rotation_step) & 7;
         consume_stage(ring_addr + static_cast<uint32_t>(slot * p.slot_stride), packed_pitch, meta_pitch,
-                      stage_k, st, xf_addr, sx_base, warp, g, t, group_parity, feeds_b, xb, acc_a, acc_b);
+                      stage_k, st, xf_addr, sx_base, vwarp, g, t, group_parity, feeds_b, xb, acc_a, acc_b);
         __syncwarp();
         if (lane == 0) mbar_arrive(&hdr->empty[slot]);
         if (++slot == p.slots) slot = 0, parity ^= 1;
