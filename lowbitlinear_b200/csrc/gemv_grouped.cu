@@ -6,7 +6,7 @@
 // bus.  Here the problems of a step are described once, on the host, as a plan in device memory:
 // per problem the three tensor maps over the reference layout, pointers and sizes; per CTA a list
 // of segments, a segment being a run of consecutive 16-row tiles of one problem.  The plan cuts
-// the byte stream of all problems into one contiguous share per CTA, so a CTA starts its pipeline
+// the stream of all problems' pipeline stages into one contiguous share per CTA, so a CTA starts its pipeline
 // once, builds an activation operand once or twice, and streams its share at the copy rate; there
 // is no tail of idle CTAs between problems and no split-K (small-N problems are simply short
 // shares of the stream).
@@ -344,7 +344,7 @@ cudaError_t group_plan_create(const GroupProblemDesc* descs, int count, int sm_c
     max_slot = std::max(max_slot, plan.slot_bytes);
     max_xf = std::max(max_xf, (g.M * g.K * 2 + 127) / 128 * 128);
     max_sx = std::max(max_sx, ((g.K / 64) * 2 * 4 + 127) / 128 * 128);
-    total_cost += static_cast<int64_t>(g.row_tiles) * g.K;
+    total_cost += static_cast<int64_t>(g.row_tiles) * g.stages_per_unit;
     bytes += d.N * d.K / 2 + 8 * d.N * (d.K / 64) + 2 * d.M * d.K + 2 * d.M * d.N;
   }
   const int red_bytes = kRedBuffers * kConsumerWarps * kRows * 4 * 4;
@@ -357,7 +357,11 @@ cudaError_t group_plan_create(const GroupProblemDesc* descs, int count, int sm_c
   }
   const int grid = 2 * sm_count;
 
-  // Cut the stream of units (cost = columns of K per unit) into `grid` contiguous shares.
+  // Cut the stream of units into `grid` contiguous shares of equal cost.  The cost of a unit is its
+  // number of pipeline stages, not its bytes: a CTA keeps a fixed number of stages in flight, so
+  // under a saturated memory system it retires stages at the same rate whatever their width, and
+  // shares with equal stage counts end together (measured on K-split shards with K = 3072 next to
+  // K = 4096: balancing by bytes left the CTAs with the narrower stages a third behind).
   std::vector<GroupSegment> segments;
   std::vector<int> first(static_cast<size_t>(grid) + 1, 0);
   {
@@ -369,12 +373,13 @@ cudaError_t group_plan_create(const GroupProblemDesc* descs, int count, int sm_c
       while (prob < count && (done < target || c == grid - 1)) {
         const GroupProblem& g = problems[static_cast<size_t>(prob)];
         const int left = g.row_tiles - rt;
+        const int64_t unit_cost = g.stages_per_unit;
         // Units of this problem that fit below the target (at least one, so that shares advance).
-        int64_t take = (target - done + g.K - 1) / g.K;
+        int64_t take = (target - done + unit_cost - 1) / unit_cost;
         if (c == grid - 1 || take > left) take = left;
         if (take < 1) take = 1;
         segments.push_back(GroupSegment{prob, rt, static_cast<int>(take), 0});
-        done += take * g.K;
+        done += take * unit_cost;
         rt += static_cast<int>(take);
         if (rt == g.row_tiles) ++prob, rt = 0;
       }
