@@ -574,12 +574,35 @@ def run_decode(ctx, layers, reference):
     if not torch.equal(after, runner.y_flat):
         raise SystemExit("the grouped launch is not bit-reproducible")
 
-    # ---- end to end: pinned host activations -> device -> one replay -> host outputs --------------
+    # ---- end to end: every step copies its activations up from pinned host memory, runs one replay
+    # and copies its outputs down; a two-deep pipeline (PipelinedLinears) overlaps the copies of
+    # neighbouring steps with the compute.  The serial form (copy, compute, copy, wait) is reported too.
+    from lowbitlinear_b200.graph import PipelinedLinears
+
     host_x = runner.x_flat.cpu().pin_memory()
     host_y = torch.zeros(runner.y_flat.numel(), dtype=torch.float16).pin_memory()
-    e2e_ms = ctx.wall_steps(lambda: runner.run(host_x, host_y), max(5, min(args.steps, 50)))
+    serial_ms = ctx.wall_steps(lambda: runner.run(host_x, host_y), max(5, min(args.steps, 50)))
     if not torch.equal(host_y, after.cpu()):
         raise SystemExit("end-to-end outputs differ from the device-timed ones")
+    pipe = PipelinedLinears(modules, m=1, reduce=reduce, exchange=exchange)
+    host_ys = [torch.zeros_like(host_y).pin_memory() for _ in range(3)]
+    e2e_steps = max(10, min(args.steps, 50))
+
+    def pipelined_pass(steps):
+        for i in range(steps):
+            pipe.submit(host_x, host_ys[i % 3])
+        pipe.drain()
+
+    pipelined_pass(6)
+    ctx.barrier()
+    t0 = time.perf_counter()
+    pipelined_pass(e2e_steps)
+    ctx.barrier()
+    e2e_ms = ctx.max_over_ranks((time.perf_counter() - t0) * 1e3 / e2e_steps)
+    for buf in host_ys:
+        if not torch.equal(buf, after.cpu()):
+            raise SystemExit("pipelined end-to-end outputs differ from the device-timed ones")
+    del pipe
 
     # ---- secondary: one launch per linear (what a model with dependent layers would do) -----------
     per_linear = None
@@ -631,8 +654,10 @@ def run_decode(ctx, layers, reference):
              "roofline": roofline, "clocks": clocks,
              "e2e": {"value": amount / (e2e_ms * 1e-3), "unit": unit, "ms_per_step": e2e_ms,
                      "h2d_bytes_per_step": int(host_x.numel() * 2), "d2h_bytes_per_step": int(host_y.numel() * 2),
-                     "api": "lowbitlinear_b200.graph.GraphedLinears.run: pinned host activations in, one CUDA-graph "
-                            "replay (one grouped launch), host outputs out"},
+                     "api": "lowbitlinear_b200.graph.PipelinedLinears.submit: per step pinned host activations in, one "
+                            "CUDA-graph replay (one grouped launch), host outputs out; two steps in flight",
+                     "serial_ms_per_step": serial_ms,
+                     "serial_api": "GraphedLinears.run: copy in, replay, copy out, wait -- one step at a time"},
              "gpu_launches": launches * args.steps,
              "launch": ("one grouped launch (lbl_w4a16_group_run) over the 144 independent linears"
                         + ("" if world == 1 else " + one all-reduce kernel over NVLink peer memory for the 36 Down outputs")),

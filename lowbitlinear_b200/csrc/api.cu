@@ -234,7 +234,7 @@ int run_linear(const void* X, const int32_t* packed_w, const float* scales, cons
       if (!lbl::gemm_tc_supports(M, N, K)) {
         return fail(LBL_ERR_UNSUPPORTED, "tensor-core GEMM cannot serve M=%lld N=%lld K=%lld (needs N %% 256 == 0, K %% 256 == 0)", (long long)M, (long long)N, (long long)K);
       }
-      err = lbl::launch_gemm_tc(prob, info.status_word, cu_stream);
+      err = lbl::launch_gemm_tc(prob, info.status_word, cu_stream, (flags & LBL_FLAG_PDL) != 0);
       break;
     }
     case LBL_PATH_GEMM_TC_SMALL: {

@@ -27,6 +27,8 @@
 // Each weight is dequantised once per 256 rows of X (about 2.6 instructions per weight for the
 // exact policy).
 // Every wait on an mbarrier is bounded; a timeout sets the device status word and the CTA drains.
+// With programmatic dependent launch the set-up and the weights of the first stages overlap the
+// previous kernel in the stream; the X loads and the outputs wait for it.
 // Shapes: N % 256 == 0 and K % 256 == 0; any M >= 1.  No cluster launch, no multicast.
 #include "kernels.h"
 #include "tc_common.cuh"
@@ -107,10 +109,15 @@ __global__ void __launch_bounds__(kThreads, 1)
   __syncthreads();
   tc_fence_after_sync();
   const uint32_t tmem_base = *reinterpret_cast<volatile uint32_t*>(&bars->tmem_base);
+  // Programmatic dependent launch (no-ops without it): the next kernel in the stream may set itself
+  // up while this one runs; in this one only the activations and the outputs depend on the kernel
+  // before, so the weights are fetched and dequantised without waiting.
+  pdl_allow_next_kernel();
 
   if (warp == 0) {
     // ------------------------------- TMA producer (X blocks) ---------------------------------
     if (lane == 0) {
+      pdl_wait_for_previous_kernel();
       for (int kb = 0; kb < k_blocks; ++kb) {
         const int s = kb % kStages;
         const int round = kb / kStages;
@@ -156,6 +163,7 @@ __global__ void __launch_bounds__(kThreads, 1)
     // ------------------------------- epilogue ---------------------------------------------------
     const bool ok = mbar_wait_bounded(&bars->acc_full, 0, abort_flag, p.status, kStatusGemmWait + 5);
     tc_fence_after_sync();
+    pdl_wait_for_previous_kernel();  // before the first write to Y
     const int quarter = warp & 3;        // TMEM lanes this warp may read
     const int h = ((warp - 2) >> 2) & 1;  // accumulator handled by this warp
     const int column_half = (warp - 2) >> 3;  // two warps share a quarter of an accumulator
@@ -207,7 +215,7 @@ bool gemm_tc_supports(int64_t M, int64_t N, int64_t K) {
          N <= (1 << 24) && K <= (1 << 24) && (N / kBN) * ((M + kBM - 1) / kBM) <= 0x7fffffffLL;
 }
 
-cudaError_t launch_gemm_tc(const Problem& p, int* status_word, cudaStream_t stream) {
+cudaError_t launch_gemm_tc(const Problem& p, int* status_word, cudaStream_t stream, bool pdl) {
   CUtensorMap tmap;
   const uint64_t dims[2] = {static_cast<uint64_t>(p.K), static_cast<uint64_t>(p.M)};
   const uint64_t strides[1] = {static_cast<uint64_t>(p.K) * sizeof(__half)};
@@ -239,8 +247,17 @@ cudaError_t launch_gemm_tc(const Problem& p, int* status_word, cudaStream_t stre
   gp.m_tiles = static_cast<int>((p.M + kBM - 1) / kBM);
   gp.status = status_word;
   const unsigned grid = static_cast<unsigned>((p.N / kBN) * gp.m_tiles);
-  w4a16_gemm_tc_kernel<<<grid, kThreads, kSmemBytes, stream>>>(tmap, gp);
-  return cudaGetLastError();
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3(grid);
+  cfg.blockDim = dim3(kThreads);
+  cfg.dynamicSmemBytes = kSmemBytes;
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = pdl ? 1 : 0;
+  return cudaLaunchKernelEx(&cfg, w4a16_gemm_tc_kernel, tmap, gp);
 }
 
 }  // namespace lbl

@@ -125,7 +125,7 @@ cudaError_t launch_gemv_grouped(const GroupPlan* plan, bool pdl, cudaStream_t st
 
 // ----- TMA + tcgen05 GEMM (gemm_tc.cu) ---------------------------------------------------------
 bool gemm_tc_supports(int64_t M, int64_t N, int64_t K);
-cudaError_t launch_gemm_tc(const Problem& p, int* status_word, cudaStream_t stream);
+cudaError_t launch_gemm_tc(const Problem& p, int* status_word, cudaStream_t stream, bool pdl);
 
 // ----- tcgen05 GEMM for M <= 128, weights on the M side of the MMA (gemm_tc_small.cu) ----------
 bool gemm_tc_small_supports(int64_t M, int64_t N, int64_t K);

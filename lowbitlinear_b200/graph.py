@@ -128,3 +128,59 @@ class GraphedLinears:
         host_y.copy_(self.y_flat, non_blocking=True)
         torch.cuda.current_stream(self.device).synchronize()
         return host_y
+
+
+class PipelinedLinears:
+    """Two ``GraphedLinears`` over the same layers with separate static buffers, driven as a
+    two-deep pipeline: while step *i* computes, the activations of step *i + 1* are copied up and
+    the outputs of step *i - 1* are copied down, on a copy stream of their own.
+
+        pipe = PipelinedLinears(layers, m=1)
+        for host_x, host_y in steps:            # pinned flat FP16 buffers, two or more pairs in rotation
+            pipe.submit(host_x, host_y)         # returns once step i is queued; step i - 2 has landed
+        pipe.drain()                            # every submitted host_y is complete
+
+    Every step still does its own host-to-device and device-to-host copy; only the waiting
+    overlaps.  A ``host_y`` may be read after the second ``submit`` that follows its own, or after
+    ``drain``.  Weights are shared between the two runners; the extra cost is a second set of
+    activation and output buffers."""
+
+    def __init__(self, layers, m=1, **kwargs):
+        self.runners = [GraphedLinears(layers, m=m, **kwargs) for _ in range(2)]
+        self.device = self.runners[0].device
+        self.up_stream = torch.cuda.Stream(device=self.device)
+        self.down_stream = torch.cuda.Stream(device=self.device)
+        self.compute_stream = torch.cuda.Stream(device=self.device)
+        self.uploaded = [torch.cuda.Event() for _ in range(2)]
+        self.computed = [torch.cuda.Event() for _ in range(2)]
+        self.downloaded = [torch.cuda.Event() for _ in range(2)]
+        self.steps = 0
+
+    def submit(self, host_x, host_y):
+        slot = self.steps & 1
+        runner = self.runners[slot]
+        reused = self.steps >= 2
+        if reused:
+            # Bound the queue: the host runs at most two steps ahead of the copies coming back.
+            self.downloaded[slot].synchronize()
+        with torch.cuda.stream(self.up_stream):
+            if reused:
+                self.up_stream.wait_event(self.computed[slot])  # the slot's activations have been read
+            runner.x_flat.copy_(host_x, non_blocking=True)
+            self.uploaded[slot].record(self.up_stream)
+        with torch.cuda.stream(self.compute_stream):
+            self.compute_stream.wait_event(self.uploaded[slot])
+            if reused:
+                self.compute_stream.wait_event(self.downloaded[slot])  # the slot's outputs have left
+            runner.graph.replay()
+            self.computed[slot].record(self.compute_stream)
+        with torch.cuda.stream(self.down_stream):
+            self.down_stream.wait_event(self.computed[slot])
+            host_y.copy_(runner.y_flat, non_blocking=True)
+            self.downloaded[slot].record(self.down_stream)
+        self.steps += 1
+
+    def drain(self):
+        self.up_stream.synchronize()
+        self.compute_stream.synchronize()
+        self.down_stream.synchronize()

@@ -119,6 +119,32 @@ def test_group_inside_a_cuda_graph_with_dependent_launch(cuda_ops):
     torch.testing.assert_close(other, host_y, atol=ATOL, rtol=RTOL)
 
 
+def test_two_deep_pipeline_matches_the_serial_runner(cuda_ops):
+    """PipelinedLinears overlaps the copies of neighbouring steps with the compute; every step's
+    outputs must equal those of the serial copy-compute-copy runner on the same activations."""
+    from lowbitlinear_b200 import QuantizedLinear
+    from lowbitlinear_b200.graph import GraphedLinears, PipelinedLinears
+
+    layers = []
+    for i, (n, k) in enumerate([(512, 1024), (256, 4096), (1024, 2048), (128, 12288)] * 2):
+        _, packed, scales, zeros = seeded_layer(1, n, k, seed=60 + i, std=0.05, device=cuda_ops)
+        layers.append(QuantizedLinear(packed, scales, zeros, in_features=k))
+    serial = GraphedLinears(layers, m=1)
+    pipe = PipelinedLinears(layers, m=1)
+    steps = 7
+    host_xs = [torch.randn(serial.x_flat.numel()).half().pin_memory() for _ in range(steps)]
+    want = []
+    for hx in host_xs:
+        out = torch.zeros(serial.y_flat.numel(), dtype=torch.float16).pin_memory()
+        want.append(serial.run(hx, out).clone())
+    got = [torch.zeros(serial.y_flat.numel(), dtype=torch.float16).pin_memory() for _ in range(steps)]
+    for hx, hy in zip(host_xs, got):
+        pipe.submit(hx, hy)
+    pipe.drain()
+    for i, (a, b) in enumerate(zip(got, want)):
+        assert torch.equal(a, b), i
+
+
 def test_group_rejects_what_it_cannot_serve(cuda_ops):
     from lowbitlinear_b200 import _ops
 
