@@ -81,41 +81,6 @@ __device__ __forceinline__ bool mbar_poll(uint64_t* bar, uint32_t parity) {
   return done != 0;
 }
 
-// Non-blocking test of the phase (never parks the warp).
-__device__ __forceinline__ bool mbar_test_wait(uint64_t* bar, uint32_t parity) {
-  uint32_t done;
-  asm volatile(
-      "{\n\t.reg .pred p;\n\t"
-      "mbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
-      "selp.u32 %0, 1, 0, p;\n\t}"
-      : "=r"(done)
-      : "r"(smem_addr(bar)), "r"(parity)
-      : "memory");
-  return done != 0;
-}
-
-// The same contract as mbar_wait_bounded, but the warp keeps polling instead of parking: for the
-// few threads whose wake-up latency is on the critical path of a pipeline (an MMA issuer, a warp
-// that hands a tile to it).
-__device__ __forceinline__ bool mbar_spin_bounded(uint64_t* bar, uint32_t parity,
-                                                  volatile int* abort_flag, int* status_word,
-                                                  int status_code) {
-  if (mbar_test_wait(bar, parity)) return true;
-  const long long start = clock64();
-  while (true) {
-#pragma unroll 1
-    for (int i = 0; i < 256; ++i) {
-      if (mbar_test_wait(bar, parity)) return true;
-    }
-    if (*abort_flag) return false;
-    if (clock64() - start > kWaitLimitCycles) {
-      *abort_flag = 1;
-      atomicCAS(status_word, 0, status_code);
-      return false;
-    }
-  }
-}
-
 __device__ __forceinline__ bool mbar_wait_bounded(uint64_t* bar, uint32_t parity,
                                                   volatile int* abort_flag, int* status_word,
                                                   int status_code) {

@@ -42,11 +42,12 @@
 namespace lbl {
 namespace {
 
-#ifdef LBL_WT_SPIN
-#define WT_WAIT mbar_spin_bounded
-#else
-#define WT_WAIT mbar_wait_bounded
-#endif
+// Ablation switches (build with `python -m lowbitlinear_b200.build -D <name>`; results are then
+// wrong, only the timing means something): LBL_WT_SKIP_TMA (no copies, the barriers are arrived on
+// directly), LBL_WT_SKIP_MMA (no tcgen05.mma), LBL_WT_SKIP_DEQUANT (the dequantisation warps only
+// hand the slots on), LBL_WT_NO_ARITHMETIC (they store the raw words), LBL_WT_SKIP_EPILOGUE (no
+// output stores).  They separate the costs of the copies, the tensor pipe, the dequantisation and
+// the epilogue of a kernel in which all four overlap.
 
 constexpr int kRowsW = 256;     // weight rows per CTA: two MMA blocks of 128
 constexpr int kBK = 64;
@@ -57,9 +58,10 @@ constexpr int kMaxTokens = LBL_WT_TOKENS;
 constexpr int kMaxStages = 8;
 constexpr int kMaxASlots = 4;
 #ifndef LBL_WT_WARPS
-#define LBL_WT_WARPS 16
+#define LBL_WT_WARPS 8
 #endif
-constexpr int kDequantWarps = LBL_WT_WARPS;   // 8: one thread per weight row; 16: two, half a k-block each
+// 8: one thread per weight row; 16: two, half a k-block each (measured 8 % slower at M = 2048).
+constexpr int kDequantWarps = LBL_WT_WARPS;
 constexpr int kThreadsPerRow = kDequantWarps / 8;
 constexpr int kWordsPerThread = 8 / kThreadsPerRow;
 constexpr int kThreads = 32 * (2 + kDequantWarps);
@@ -256,8 +258,8 @@ __global__ void __launch_bounds__(kThreads, 1)
         const int round = kb / p.stages;
         const int slot = kb % p.a_slots;
         const int around = kb / p.a_slots;
-        WT_WAIT(&bars->full[s], round & 1, abort_flag, p.status, kStatusWtWait + 4);
-        WT_WAIT(&bars->a_full[slot], around & 1, abort_flag, p.status, kStatusWtWait + 5);
+        mbar_wait_bounded(&bars->full[s], round & 1, abort_flag, p.status, kStatusWtWait + 4);
+        mbar_wait_bounded(&bars->a_full[slot], around & 1, abort_flag, p.status, kStatusWtWait + 5);
         if (*abort_flag) break;
         tc_fence_after_sync();
         const uint32_t x_addr = smem_addr(smem_x + s * x_stage_bytes);
@@ -267,10 +269,7 @@ __global__ void __launch_bounds__(kThreads, 1)
 #pragma unroll
           for (int b = 0; b < 2; ++b) {
             const uint32_t a_col = a_base_col + static_cast<uint32_t>((slot * 2 + b) * 32 + kk * 8);
-#if defined(LBL_WT_SS_MMA)
-            mma_f16(tmem_base + static_cast<uint32_t>(b * p.tokens), smem_desc_k_major_sw128(x_addr + kk * 32), b_desc,
-                    idesc, (kb | kk) != 0 ? 1u : 0u);
-#elif !defined(LBL_WT_SKIP_MMA)
+#ifndef LBL_WT_SKIP_MMA
             mma_f16_ts(tmem_base + static_cast<uint32_t>(b * p.tokens), tmem_base + a_col, b_desc, idesc,
                        (kb | kk) != 0 ? 1u : 0u);
 #endif
@@ -288,10 +287,14 @@ __global__ void __launch_bounds__(kThreads, 1)
     const int part = (warp - 2) >> 3;            // which piece of the k-block's 64 columns (two threads per row)
     const int row = block * 128 + quarter * 32 + lane;  // weight row within the CTA's 256
     const uint32_t lane_base = static_cast<uint32_t>(quarter * 32) << 16;
+    // Ring positions advance by counting: a division per k-block and thread would cost as much as a
+    // third of the dequantisation itself.
+    int s = 0, full_parity = 0;            // stage of the shared-memory ring and the phase to wait for
+    int slot = 0, a_parity = 1, a_round = 0;  // A slot, phase of its `empty` barrier, rounds completed
     for (int sb = 0; sb * 4 < k_blocks; ++sb) {
       const int ms = sb & 1;
       const int mround = sb >> 1;
-      WT_WAIT(&bars->meta_full[ms], mround & 1, abort_flag, p.status, kStatusWtWait + 6);
+      mbar_wait_bounded(&bars->meta_full[ms], mround & 1, abort_flag, p.status, kStatusWtWait + 6);
       const uint8_t* meta = smem_meta + ms * kMetaSlotBytes + row * 16;
       const uint4 scale_bits = lds128_generic(meta);
       const uint4 zero_bits = lds128_generic(meta + kMetaTileBytes);
@@ -303,10 +306,7 @@ __global__ void __launch_bounds__(kThreads, 1)
                          static_cast<int>(zero_bits.z), static_cast<int>(zero_bits.w)};
 #pragma unroll
       for (int j = 0; j < 4; ++j) {
-        const int kb = sb * 4 + j;
-        const int s = kb % p.stages;
-        const int round = kb / p.stages;
-        WT_WAIT(&bars->full[s], round & 1, abort_flag, p.status, kStatusWtWait + 7);
+        mbar_wait_bounded(&bars->full[s], full_parity, abort_flag, p.status, kStatusWtWait + 7);
         const uint8_t* words = smem_w + s * kPackedTileBytes + row * kPackedPitch + part * 16;
         uint32_t w[kWordsPerThread];
         {
@@ -320,16 +320,16 @@ __global__ void __launch_bounds__(kThreads, 1)
         }
         __syncwarp();
         if (lane == 0) mbar_arrive(&bars->w_empty[s]);
-        const int slot = kb % p.a_slots;
-        const int around = kb / p.a_slots;
-        if (around > 0) {
-          WT_WAIT(&bars->a_empty[slot], (around - 1) & 1, abort_flag, p.status, kStatusWtWait + 8);
+        if (a_round > 0) {
+          mbar_wait_bounded(&bars->a_empty[slot], a_parity, abort_flag, p.status, kStatusWtWait + 8);
           tc_fence_after_sync();
         }
 #ifdef LBL_WT_SKIP_DEQUANT
         tc_fence_before_sync();
         __syncwarp();
         if (lane == 0) mbar_arrive(&bars->a_full[slot]);
+        if (++s == p.stages) s = 0, full_parity ^= 1;
+        if (++slot == p.a_slots) slot = 0, a_parity ^= 1, ++a_round;
         continue;
 #endif
         const GroupConstants group = group_constants(sc[j], zp[j]);
@@ -350,6 +350,8 @@ __global__ void __launch_bounds__(kThreads, 1)
         tc_fence_before_sync();
         __syncwarp();
         if (lane == 0) mbar_arrive(&bars->a_full[slot]);
+        if (++s == p.stages) s = 0, full_parity ^= 1;
+        if (++slot == p.a_slots) slot = 0, a_parity ^= 1, ++a_round;
       }
     }
 
