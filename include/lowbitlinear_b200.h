@@ -49,6 +49,9 @@ extern "C" {
 #define LBL_PATH_GEMM_WT 6       /* tcgen05 GEMM, weights dequantised in registers and handed to the
                                     MMA through tensor memory (any M; K sliced when M is small)  */
 
+#define LBL_PATH_GEMM_TC_PAIR 7 /* the tcgen05 GEMM on pairs of CTAs (cta_group::2): a 512 x 256 tile per
+                                    pair that shares one dequantised copy of the weights            */
+
 /* Flags. */
 #define LBL_FLAG_PDL 1u            /* programmatic dependent launch: weights are prefetched
                                       before the previous kernel in the stream has finished.

@@ -14,7 +14,7 @@ import threading
 
 import torch
 
-PATH_AUTO, PATH_GENERIC, PATH_GEMV, PATH_GEMV_SPLITK, PATH_GEMM_TC, PATH_GEMM_TC_SMALL, PATH_GEMM_WT = range(7)
+PATH_AUTO, PATH_GENERIC, PATH_GEMV, PATH_GEMV_SPLITK, PATH_GEMM_TC, PATH_GEMM_TC_SMALL, PATH_GEMM_WT, PATH_GEMM_TC_PAIR = range(8)
 PATH_NAMES = {
     PATH_AUTO: "auto",
     PATH_GENERIC: "generic",
@@ -23,6 +23,7 @@ PATH_NAMES = {
     PATH_GEMM_TC: "gemm_tc",
     PATH_GEMM_TC_SMALL: "gemm_tc_small",
     PATH_GEMM_WT: "gemm_wt",
+    PATH_GEMM_TC_PAIR: "gemm_tc_pair",
 }
 FLAG_PDL = 1
 FLAG_ROUND_WEIGHTS = 2

@@ -22,7 +22,7 @@ except ImportError:  # run as a plain script
     from _fingerprint import BUILD_DIR, CSRC, DEFINES, INCLUDE, PACKAGE_DIR, STAMP, source_fingerprint
 
 OUTPUT = PACKAGE_DIR / "_C.so"
-SOURCES = ("api.cu", "generic.cu", "skinny.cu", "gemv_decode.cu", "gemv_grouped.cu", "peer_reduce.cu", "gemm_tc.cu", "gemm_tc_small.cu", "gemm_wt.cu", "quantize.cu",
+SOURCES = ("api.cu", "generic.cu", "skinny.cu", "gemv_decode.cu", "gemv_grouped.cu", "peer_reduce.cu", "gemm_tc.cu", "gemm_tc2.cu", "gemm_tc_small.cu", "gemm_wt.cu", "quantize.cu",
            "tensor_map.cu")
 ARCH_FLAGS = ("-gencode", "arch=compute_100a,code=sm_100a")
 COMMON_FLAGS = ("-O3", "-std=c++17", "-lineinfo", "-Xcompiler", "-fPIC", "-Xptxas", "-v")

@@ -126,8 +126,12 @@ __global__ void __launch_bounds__(kThreads, 1)
                             kStatusGemmWait + 1);
         }
         if (*abort_flag) break;
+#ifdef LBL_TC_SKIP_TMA  // ablation switch
+        mbar_arrive(&bars->a_full[s]);
+#else
         mbar_arrive_expect_tx(&bars->a_full[s], kStageBytesA);
         tma_load_2d(smem_a + s * kStageBytesA, &tmap_x, kb * kBK, m0, &bars->a_full[s]);
+#endif
       }
     }
   } else if (warp == 1) {
@@ -147,7 +151,9 @@ __global__ void __launch_bounds__(kThreads, 1)
           const uint64_t b_desc = smem_desc_k_major_sw128(b_addr + kk * 32);
           for (int h = 0; h < halves; ++h) {
             const uint64_t a_desc = smem_desc_k_major_sw128(a_addr + h * (128 * 128) + kk * 32);
+#ifndef LBL_TC_SKIP_MMA  // ablation switch
             mma_f16(tmem_base + h * kBN, a_desc, b_desc, kInstrDesc, (kb | kk) != 0 ? 1u : 0u);
+#endif
           }
         }
         mma_commit(&bars->empty[s]);  // frees the stage once these MMAs have read it

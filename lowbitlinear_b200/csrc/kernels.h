@@ -136,6 +136,10 @@ cudaError_t launch_gemm_tc_small(const Problem& p, int* status_word, cudaStream_
                                  size_t workspace_bytes, int sm_count, bool pdl);
 
 
+// ----- TMA + tcgen05 GEMM on pairs of CTAs, cta_group::2 (gemm_tc2.cu) ---------------------------
+bool gemm_tc_pair_supports(int64_t M, int64_t N, int64_t K);
+cudaError_t launch_gemm_tc_pair(const Problem& p, int* status_word, cudaStream_t stream);
+
 // ----- tcgen05 GEMM with the weights passed through tensor memory (gemm_wt.cu) ------------------
 bool gemm_wt_supports(int64_t M, int64_t N, int64_t K);
 // Scratch that lets K be cut into slices when there are few tokens and few row blocks (0: none).

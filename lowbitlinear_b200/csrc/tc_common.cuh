@@ -120,45 +120,66 @@ __device__ __forceinline__ uint4 dequant_word(uint32_t word, const GroupConstant
 }
 
 // ---- the dequantisation worker shared by the tensor-core kernels ------------------------------
-// Two threads own one weight row of the K-major, 128-byte-swizzled tile, half a group (32 columns)
-// each.  A thread keeps the packed words of two super blocks (256 columns: four groups, four words
-// of each) and the row's metadata in registers, one being consumed while the next is in flight.
-struct HalfRowPrefetch {
-  uint4 words[4];
+// Two or four threads own one weight row of the K-major, 128-byte-swizzled tile.  A thread keeps
+// its packed words of two super blocks (256 columns: four groups) and the row's metadata in
+// registers, one super block being consumed while the next is in flight.
+// Registers that hold a thread's share of one super block (256 columns: four groups) of its row:
+// kWords packed words of each of the four k-blocks, and the row's metadata.
+template <int kWords>
+struct RowPrefetch {
+  uint32_t words[4][kWords];
   float4 scale;
   int4 zero;
 };
 
-// Walks super blocks [sb_begin, sb_end) of weight row `n`.  For its j-th k-block (one group) it
-// waits until ring stage j % kStages is free, writes its 32 dequantised weights into the stage's
-// tile at `tiles + stage * kStageBytes`, fences the async proxy and arrives (one arrival per warp)
-// on full[stage].  `worker` is the thread's index among the dequantisation threads (row = worker
-// / 2, half = worker % 2); `status_code` is reported if a wait on `empty` expires.
-template <int kStages, int kStageBytes>
+// Walks super blocks [sb_begin, sb_end) of weight row `n`.  kThreadsPerRow (2 or 4) threads own one
+// weight row of the K-major, 128-byte-swizzled tile, 32 or 16 columns of every k-block each.  For
+// its j-th k-block (one group) a thread waits until ring stage j % kStages is free, writes its
+// dequantised weights into the stage's tile at `tiles + stage * kStageBytes`, fences the async
+// proxy and arrives (one arrival per warp) on full[stage].  `worker` is the thread's index among
+// the dequantisation threads (row = worker / kThreadsPerRow); `status_code` is reported if a wait
+// on `empty` expires.  With `full_cluster_base` != 0 the arrival goes to that shared::cluster
+// address + 8 * stage instead (the barrier of the first CTA of a pair), with release semantics at
+// cluster scope.
+template <int kStages, int kStageBytes, int kThreadsPerRow = 2>
 __device__ __forceinline__ void dequantise_rows(const uint32_t* packed, const float* scales,
                                                 const int32_t* zeros, int K, size_t n0, int worker,
                                                 int sb_begin, int sb_end, uint8_t* tiles,
                                                 uint64_t* full, uint64_t* empty,
-                                                volatile int* abort_flag, int* status, int status_code) {
+                                                volatile int* abort_flag, int* status, int status_code,
+                                                uint32_t full_cluster_base = 0) {
+  static_assert(kThreadsPerRow == 2 || kThreadsPerRow == 4, "two or four threads per weight row");
+  constexpr int kWords = 8 / kThreadsPerRow;  // packed words per thread and k-block
   const int lane = threadIdx.x & 31;
-  const int row = worker >> 1;
-  const int half = worker & 1;
+  const int row = worker / kThreadsPerRow;
+  const int part = worker % kThreadsPerRow;
   const size_t n = n0 + row;
-  const uint32_t* packed_row = packed + n * (K / 8) + half * 4;
+  const uint32_t* packed_row = packed + n * (K / 8) + part * kWords;
   const float* scale_row = scales + n * (K / 64);
   const int32_t* zero_row = zeros + n * (K / 64);
   const uint32_t row_offset = (row >> 3) * 1024 + (row & 7) * 128;
   const uint32_t swz = row & 7;
 
-  auto prefetch = [&](HalfRowPrefetch& buf, int super_block) {
+  auto prefetch = [&](RowPrefetch<kWords>& buf, int super_block) {
+#ifdef LBL_TC_SKIP_DEQUANT
+    return;
+#endif
     const uint32_t* src = packed_row + super_block * 32;
 #pragma unroll
-    for (int j = 0; j < 4; ++j) buf.words[j] = __ldg(reinterpret_cast<const uint4*>(src + j * 8));
+    for (int j = 0; j < 4; ++j) {
+      if constexpr (kWords == 4) {
+        const uint4 v = __ldg(reinterpret_cast<const uint4*>(src + j * 8));
+        buf.words[j][0] = v.x, buf.words[j][1] = v.y, buf.words[j][2] = v.z, buf.words[j][3] = v.w;
+      } else {
+        const uint2 v = __ldg(reinterpret_cast<const uint2*>(src + j * 8));
+        buf.words[j][0] = v.x, buf.words[j][1] = v.y;
+      }
+    }
     buf.scale = __ldg(reinterpret_cast<const float4*>(scale_row + super_block * 4));
     buf.zero = __ldg(reinterpret_cast<const int4*>(zero_row + super_block * 4));
   };
   // `sb` counts this CTA's super blocks from 0; the data come from super block sb_begin + sb.
-  auto run_super_block = [&](const HalfRowPrefetch& cur, int sb) {
+  auto run_super_block = [&](const RowPrefetch<kWords>& cur, int sb) {
     const float sc[4] = {cur.scale.x, cur.scale.y, cur.scale.z, cur.scale.w};
     const int zp[4] = {cur.zero.x, cur.zero.y, cur.zero.z, cur.zero.w};
 #pragma unroll
@@ -167,22 +188,36 @@ __device__ __forceinline__ void dequantise_rows(const uint32_t* packed, const fl
       const int s = kb % kStages;
       const int round = kb / kStages;
       if (round > 0) mbar_wait_bounded(&empty[s], (round - 1) & 1, abort_flag, status, status_code);
+#ifndef LBL_TC_SKIP_DEQUANT  // ablation switch: the warps only hand the stages on
       const GroupConstants group = group_constants(sc[j], zp[j]);
       uint8_t* dst = tiles + s * kStageBytes + row_offset;
-      const uint32_t w[4] = {cur.words[j].x, cur.words[j].y, cur.words[j].z, cur.words[j].w};
 #pragma unroll
-      for (int c = 0; c < 4; ++c) {
-        const uint4 out = dequant_word(w[c], group);
-        *reinterpret_cast<uint4*>(dst + ((static_cast<uint32_t>(half * 4 + c) ^ swz) << 4)) = out;
+      for (int c = 0; c < kWords; ++c) {
+#ifdef LBL_TC_NO_ARITHMETIC  // ablation switch: loads and stores, no arithmetic
+        const uint4 out = make_uint4(cur.words[j][c], cur.words[j][c] >> 4, __float_as_uint(group.s01.x),
+                                     __float_as_uint(group.neg_c01.x));
+#else
+        const uint4 out = dequant_word(cur.words[j][c], group);
+#endif
+        *reinterpret_cast<uint4*>(dst + ((static_cast<uint32_t>(part * kWords + c) ^ swz) << 4)) = out;
       }
+#endif
       fence_async_proxy();  // generic-proxy writes -> visible to the tensor core's reads
       __syncwarp();
-      if (lane == 0) mbar_arrive(&full[s]);
+      if (lane == 0) {
+        if (full_cluster_base != 0) {
+          asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(
+                           full_cluster_base + 8u * static_cast<uint32_t>(s))
+                       : "memory");
+        } else {
+          mbar_arrive(&full[s]);
+        }
+      }
     }
   };
 
   const int super_blocks = sb_end - sb_begin;
-  HalfRowPrefetch buf[2];
+  RowPrefetch<kWords> buf[2];
   prefetch(buf[0], sb_begin);
   for (int sb = 0; sb < super_blocks; sb += 2) {
     if (sb + 1 < super_blocks) prefetch(buf[1], sb_begin + sb + 1);

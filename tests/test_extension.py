@@ -133,7 +133,8 @@ def test_dispatcher_choices_and_scratch_sizes():
         assert name(1, 512, 4096) == "gemv_splitk"     # a tensor-parallel shard: 32 row tiles
         assert name(8, 4096, 12288) == "gemv_splitk"   # activations of one segment must fit on chip
         # Prefill shapes go to the tensor cores; ragged shapes to the masked kernel.
-        assert name(2048, 24576, 4096) == "gemm_tc"
+        assert name(2048, 24576, 4096) == "gemm_tc_pair"   # pairs of CTAs share the dequantised weights
+        assert name(256, 24576, 4096) == "gemm_tc"
         assert name(128, 4096, 12288) == "gemm_tc_small"   # weights on the M side of the MMA
         assert name(16, 24576, 4096) == "gemm_tc_small"
         assert name(64, 24576, 4096) == "gemm_tc"          # wide N: 256-wide tiles fill the SMs
@@ -142,7 +143,7 @@ def test_dispatcher_choices_and_scratch_sizes():
         assert name(129, 4096, 12288) == "gemm_wt"
         assert name(512, 4096, 12288) == "gemm_wt"
         assert name(2048, 512, 4096) == "gemm_wt"           # a tensor-parallel shard of O
-        assert name(2048, 4096, 12288) == "gemm_tc"
+        assert name(2048, 4096, 12288) == "gemm_tc_pair"
         assert name(300, 384, 512) == "gemm_wt"
         assert name(5, 9, 70) == "generic"
         assert name(1, 129, 64) == "generic"

@@ -159,6 +159,24 @@ def test_tensor_memory_path_against_oracle(m, n, k, cuda_ops):
     torch.testing.assert_close(unsliced.cpu(), expected, atol=atol, rtol=RTOL)
 
 
+@pytest.mark.parametrize("m,n,k", [(1, 256, 256), (16, 512, 256), (130, 256, 512), (512, 1024, 1024), (300, 512, 256),
+                                   (700, 1536, 2048), (1100, 768, 1024), (513, 256, 4096)])
+def test_paired_tensor_core_path_against_oracle(m, n, k, cuda_ops):
+    """tcgen05 GEMM on pairs of CTAs (cta_group::2): 512 tokens x 256 weight rows per pair, each CTA
+    dequantising half of the weight rows; token tails, several tiles, bit-reproducible."""
+    from lowbitlinear_b200 import _ops
+
+    x, packed, scales, zeros = seeded_layer(m, n, k, seed=m + n + k, std=1.0, device=cuda_ops)
+    runs = [_ops.linear_forced(x, packed, scales, zeros, _ops.PATH_GEMM_TC_PAIR) for _ in range(3)]
+    assert all(taken == _ops.PATH_GEMM_TC_PAIR for _, taken in runs)
+    assert torch.equal(runs[0][0], runs[1][0]) and torch.equal(runs[0][0], runs[2][0])
+    atol = ATOL * (4 if k > 2048 else 1)
+    torch.testing.assert_close(runs[0][0].cpu(), oracle_linear(x, packed, scales, zeros, mma=True), atol=atol, rtol=RTOL)
+    # Same arithmetic as the single-CTA kernel (FP16-rounded weights, FP32 accumulation in K order).
+    single, _ = _ops.linear_forced(x, packed, scales, zeros, _ops.PATH_GEMM_TC)
+    assert torch.equal(single, runs[0][0])
+
+
 def test_fp16_operand_policy_of_the_tensor_memory_kernel(cuda_ops):
     """One-hot activations pick single weights: the result must equal the FP16-rounded-weight oracle
     bit for bit (and differ from the FP32-weight one)."""
@@ -194,7 +212,8 @@ def test_prefill_shapes_meet_the_benchmark_tolerance(name, n, k, seed, m, cuda_o
 
     x, packed, scales, zeros = seeded_layer(m, n, k, seed=seed, device=cuda_ops)
     small = m <= 32 or (m <= 128 and n < 16384)
-    assert _ops.select_path(m, n, k) == (_ops.PATH_GEMM_TC_SMALL if small else _ops.PATH_GEMM_TC)
+    large = _ops.PATH_GEMM_TC_PAIR if m >= 512 else _ops.PATH_GEMM_TC
+    assert _ops.select_path(m, n, k) == (_ops.PATH_GEMM_TC_SMALL if small else large)
     layer = QuantizedLinear(packed, scales, zeros, in_features=k)
     y = layer(x)
     assert_north_star_parity(y, torch_fp32_linear(x, packed, scales, zeros))
@@ -254,7 +273,7 @@ def test_prefill_sweep_ends_meet_the_benchmark_tolerance(name, m, cuda_ops):
     # slices takes it; everything else here fills the SMs with the large tiles.
     tiles = (n // 256) * ((m + 255) // 256)
     few_tiles = 3 * tiles <= 148 or (2 * tiles <= 148 and k >= 8192)
-    assert _ops.select_path(m, n, k) == (_ops.PATH_GEMM_WT if few_tiles else _ops.PATH_GEMM_TC)
+    assert _ops.select_path(m, n, k) == (_ops.PATH_GEMM_WT if few_tiles else _ops.PATH_GEMM_TC_PAIR)
     layer = QuantizedLinear(packed, scales, zeros, in_features=k)
     y = layer(x)
     assert_north_star_parity(y, torch_fp32_linear(x, packed, scales, zeros))
