@@ -103,7 +103,6 @@ int forced_path_from_env() {
 // the large tensor-core GEMM takes what the small one cannot.
 constexpr int kTcMinM = 17;
 constexpr int kTcSmallMinM = 9;
-constexpr int kTcPairMinM = 512;
 
 int select_path(int64_t M, int64_t N, int64_t K, int op, int sm_count) {
   (void)op;
@@ -127,9 +126,17 @@ int select_path(int64_t M, int64_t N, int64_t K, int op, int sm_count) {
     // enough for eight slices.
     if (!tc_ok || 3 * tc_ctas <= sm_count || (2 * tc_ctas <= sm_count && K >= 8192)) return LBL_PATH_GEMM_WT;
   }
-  // From 512 rows of activations on, pairs of CTAs that share one dequantised copy of the weights
-  // (measured 3 - 13 % faster than single CTAs at M = 512 .. 8192 on the four benchmark shapes).
-  if (tc_ok && M >= kTcPairMinM && lbl::gemm_tc_pair_supports(M, N, K)) return LBL_PATH_GEMM_TC_PAIR;
+  // Pairs of CTAs that share one dequantised copy of the weights run a k-block in 0.83 of the time
+  // of single CTAs (measured, M = 384 .. 8192 on the benchmark shapes), but their tile holds 512
+  // tokens instead of 256: whichever needs fewer (weighted) waves of the SMs wins.
+  if (tc_ok && M > 128 && lbl::gemm_tc_pair_supports(M, N, K)) {
+    const int64_t pair_slots = sm_count >= 2 ? sm_count / 2 : 1;
+    const int64_t pairs = (N / 256) * ((M + 511) / 512);
+    const int64_t tc_ctas = (N / 256) * ((M + 255) / 256);
+    const int64_t waves_pair = (pairs + pair_slots - 1) / pair_slots;
+    const int64_t waves_tc = (tc_ctas + sm_count - 1) / sm_count;
+    if (10 * waves_pair <= 12 * waves_tc) return LBL_PATH_GEMM_TC_PAIR;
+  }
   if (tc_ok && (M >= kTcMinM || (wide && M >= 9) || !skinny_ok)) return LBL_PATH_GEMM_TC;
   if (skinny_ok) {
     lbl::SkinnyPlan plan;

@@ -19,10 +19,10 @@
 //   * per k-block a CTA holds 32 KB of X and 16 KB of weights, in two rings of four stages each
 //     (gemm_tc.cu has room for three).
 //
-// Synchronisation across the pair: the X copies of both CTAs complete on the first CTA's barrier
-// (the copy's .cta_group::2 form), the dequantisation warps of the second CTA arrive on the first
-// CTA's barrier through its shared::cluster address, one thread of the first CTA issues the MMAs,
-// and tcgen05.commit in its cluster-wide form releases a stage (and announces the finished
+// Synchronisation across the pair: each CTA tracks its own copies and warps on its own barriers;
+// one thread of the second CTA reports each finished k-block to the first CTA with a single remote
+// arrival (shared::cluster address), one thread of the first CTA issues the MMAs, and
+// tcgen05.commit in its cluster-wide form releases a stage (and announces the finished
 // accumulators) in both CTAs.  Each CTA issues its own copies, each with one destination.  Every
 // wait on an mbarrier is bounded; the pair meets at a cluster barrier before it releases tensor
 // memory.  Shapes: N % 256 == 0 and K % 256 == 0; any M >= 1.
@@ -63,11 +63,13 @@ constexpr int kBarrierBytes = 256;
 constexpr int kSmemBytes = kStagesA * kStageBytesA + kStagesB * kStageBytesB + kBarrierBytes + 1024;
 constexpr int kStatusPairWait = 500;
 
+constexpr int kRelaySlots = 4;
 struct Barriers {
-  uint64_t a_full[kStagesA];   // first CTA's: X blocks of both CTAs have landed
-  uint64_t a_empty[kStagesA];  // each CTA's own: the MMAs have read the X stage (cluster-wide commit)
-  uint64_t b_full[kStagesB];   // first CTA's: both CTAs have dequantised their rows
-  uint64_t b_empty[kStagesB];  // each CTA's own: the MMAs have read the weight stage
+  uint64_t a_full[kStagesA];   // this CTA's X blocks have landed
+  uint64_t a_empty[kStagesA];  // the MMAs have read the X stage (cluster-wide commit)
+  uint64_t b_full[kStagesB];   // this CTA's warps have dequantised their rows
+  uint64_t b_empty[kStagesB];  // the MMAs have read the weight stage (cluster-wide commit)
+  uint64_t peer_ready[kRelaySlots];  // first CTA's: the second CTA's k-block is complete
   uint64_t acc_full;         // each CTA's own
   uint32_t tmem_base;
   int abort_flag;
@@ -111,16 +113,6 @@ __device__ __forceinline__ void tmem_relinquish_pair() {
 }
 __device__ __forceinline__ void tmem_dealloc_pair(uint32_t taddr, uint32_t cols) {
   asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;" ::"r"(taddr), "r"(cols) : "memory");
-}
-// The copy lands in this CTA's shared memory; its bytes are counted on a barrier given by a
-// shared::cluster address (the first CTA's).  One destination per copy.
-__device__ __forceinline__ void tma_load_2d_pair(void* smem_dst, const CUtensorMap* map, int c0, int c1,
-                                                 uint32_t bar_cluster_addr) {
-  asm volatile(
-      "cp.async.bulk.tensor.2d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes "
-      "[%0], [%1, {%2, %3}], [%4];" ::"r"(smem_addr(smem_dst)),
-      "l"(map), "r"(c0), "r"(c1), "r"(bar_cluster_addr)
-      : "memory");
 }
 __device__ __forceinline__ void mma_f16_pair(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc,
                                              uint32_t accumulate) {
@@ -191,9 +183,10 @@ __global__ void __launch_bounds__(kThreads, 1)
       mbar_init(&bars->a_empty[s], 1);
     }
     for (int s = 0; s < kStagesB; ++s) {
-      mbar_init(&bars->b_full[s], 2 * kDequantWarps);
+      mbar_init(&bars->b_full[s], kDequantWarps);
       mbar_init(&bars->b_empty[s], 1);
     }
+    for (int s = 0; s < kRelaySlots; ++s) mbar_init(&bars->peer_ready[s], 1);
     mbar_init(&bars->acc_full, 1);
     bars->abort_flag = 0;
     mbar_init_fence();
@@ -208,8 +201,7 @@ __global__ void __launch_bounds__(kThreads, 1)
   cluster_sync_all();
   tc_fence_after_sync();
   const uint32_t tmem_base = *reinterpret_cast<volatile uint32_t*>(&bars->tmem_base);
-  const uint32_t a_full_leader = map_to_cta(smem_addr(&bars->a_full[0]), 0);
-  const uint32_t b_full_leader = map_to_cta(smem_addr(&bars->b_full[0]), 0);
+  const uint32_t peer_ready_leader = map_to_cta(smem_addr(&bars->peer_ready[0]), 0);
 
   if (warp == 0) {
     // ------------------------------- TMA producer (this CTA's X rows) ---------------------------
@@ -221,22 +213,38 @@ __global__ void __launch_bounds__(kThreads, 1)
           mbar_wait_bounded(&bars->a_empty[s], (round - 1) & 1, abort_flag, p.status, kStatusPairWait + 1);
         }
         if (*abort_flag) break;
-        // The first CTA's barrier expects the X blocks of both CTAs.
-        if (rank == 0) mbar_arrive_expect_tx(&bars->a_full[s], 2 * kStageBytesA);
+        mbar_arrive_expect_tx(&bars->a_full[s], kStageBytesA);
         for (int g = 0; g < 2; ++g) {
-          tma_load_2d_pair(smem_a + s * kStageBytesA + g * (kStageBytesA / 2), &tmap_x, kb * kBK, m0 + g * 256,
-                           a_full_leader + 8u * s);
+          tma_load_2d(smem_a + s * kStageBytesA + g * (kStageBytesA / 2), &tmap_x, kb * kBK, m0 + g * 256,
+                      &bars->a_full[s]);
         }
       }
     }
   } else if (warp == 1) {
-    // ------------------------------- MMA issuer (first CTA only) -------------------------------
+    // ------------------------------- MMA issuer (first CTA) / relay (second CTA) ----------------
+    // All signalling across the pair goes through one thread per CTA: the second CTA's thread waits
+    // for its own copies and warps and makes ONE remote arrival per k-block (eight remote arrivals
+    // and a remote completion per copy were measured at 0.8 us per k-block with nothing else running).
+    if (lane == 0 && rank == 1) {
+      for (int kb = 0; kb < k_blocks; ++kb) {
+        const int s = kb % kStagesA;
+        const int sb = kb % kStagesB;
+        mbar_wait_bounded(&bars->a_full[s], (kb / kStagesA) & 1, abort_flag, p.status, kStatusPairWait + 6);
+        mbar_wait_bounded(&bars->b_full[sb], (kb / kStagesB) & 1, abort_flag, p.status, kStatusPairWait + 7);
+        if (*abort_flag) break;
+        asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(
+                         peer_ready_leader + 8u * static_cast<uint32_t>(kb % kRelaySlots))
+                     : "memory");
+      }
+    }
     if (lane == 0 && rank == 0) {
       for (int kb = 0; kb < k_blocks; ++kb) {
         const int s = kb % kStagesA;
         const int sb = kb % kStagesB;
-        mbar_wait_cluster_bounded(&bars->a_full[s], (kb / kStagesA) & 1, abort_flag, p.status, kStatusPairWait + 2);
-        mbar_wait_cluster_bounded(&bars->b_full[sb], (kb / kStagesB) & 1, abort_flag, p.status, kStatusPairWait + 3);
+        mbar_wait_bounded(&bars->a_full[s], (kb / kStagesA) & 1, abort_flag, p.status, kStatusPairWait + 2);
+        mbar_wait_bounded(&bars->b_full[sb], (kb / kStagesB) & 1, abort_flag, p.status, kStatusPairWait + 3);
+        mbar_wait_cluster_bounded(&bars->peer_ready[kb % kRelaySlots], (kb / kRelaySlots) & 1, abort_flag, p.status,
+                                  kStatusPairWait + 8);
         if (*abort_flag) break;
         tc_fence_after_sync();
         const uint32_t a_addr = smem_addr(smem_a + s * kStageBytesA);
@@ -263,7 +271,7 @@ __global__ void __launch_bounds__(kThreads, 1)
     dequantise_rows<kStagesB, kStageBytesB, kThreadsPerRow>(p.packed, p.scales, p.zeros, p.K,
                                            static_cast<size_t>(n0) + rank * 128, (warp - 2) * 32 + lane, 0,
                                            p.K / 256, smem_b, bars->b_full, bars->b_empty, abort_flag, p.status,
-                                           kStatusPairWait + 4, b_full_leader);
+                                           kStatusPairWait + 4);
 
     // ------------------------------- epilogue ---------------------------------------------------
     const bool ok = mbar_wait_bounded(&bars->acc_full, 0, abort_flag, p.status, kStatusPairWait + 5);
