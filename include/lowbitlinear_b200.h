@@ -62,6 +62,13 @@ extern "C" {
                                       keeps the FP32 scale: the any-shape operator then runs a
                                       tensor-core or the masked kernel instead (slower for M <= 8)  */
 
+#define LBL_FLAG_INDEPENDENT 4u    /* with LBL_FLAG_PDL: this call reads nothing that the previous kernel
+                                      in the stream writes and writes nothing that it reads or writes,
+                                      so it need not wait for it at all; its CTAs then start on the SMs
+                                      that the previous kernel's last, partial wave leaves idle.  Honoured
+                                      by the large tensor-core GEMMs (LBL_PATH_GEMM_TC, _TC_PAIR), which
+                                      use no scratch; every other path keeps waiting.               */
+
 /* Library version: major * 10000 + minor * 100 + patch. */
 int lbl_version(void);
 

@@ -27,6 +27,7 @@ PATH_NAMES = {
 }
 FLAG_PDL = 1
 FLAG_ROUND_WEIGHTS = 2
+FLAG_INDEPENDENT = 4
 
 GEMV_SCHEMA = (
     "w4a16_gemv_warp_vec(Tensor x, Tensor packed_w, Tensor scales, Tensor zeros, "
@@ -121,6 +122,15 @@ def set_programmatic_dependent_launch(enabled):
     weights -- true for inference, where weights are written once.  Off by default."""
     global _flags
     _flags = (_flags | FLAG_PDL) if enabled else (_flags & ~FLAG_PDL)
+
+
+def set_independent_launches(enabled):
+    """Together with programmatic dependent launch: declare that consecutive calls are independent
+    of each other (no call reads what the previous one writes, nor writes what it reads or writes).
+    The large tensor-core GEMMs then do not wait for the previous kernel at all, and their CTAs
+    start on the SMs that its last, partial wave leaves idle.  Off by default."""
+    global _flags
+    _flags = (_flags | FLAG_INDEPENDENT) if enabled else (_flags & ~FLAG_INDEPENDENT)
 
 
 def set_reference_gemm_policy(enabled):

@@ -245,7 +245,8 @@ int run_linear(const void* X, const int32_t* packed_w, const float* scales, cons
       if (!lbl::gemm_tc_supports(M, N, K)) {
         return fail(LBL_ERR_UNSUPPORTED, "tensor-core GEMM cannot serve M=%lld N=%lld K=%lld (needs N %% 256 == 0, K %% 256 == 0)", (long long)M, (long long)N, (long long)K);
       }
-      err = lbl::launch_gemm_tc(prob, info.status_word, cu_stream, (flags & LBL_FLAG_PDL) != 0);
+      err = lbl::launch_gemm_tc(prob, info.status_word, cu_stream, (flags & LBL_FLAG_PDL) != 0,
+                                (flags & LBL_FLAG_INDEPENDENT) != 0);
       break;
     }
     case LBL_PATH_GEMM_TC_SMALL: {
@@ -260,7 +261,8 @@ int run_linear(const void* X, const int32_t* packed_w, const float* scales, cons
       if (!lbl::gemm_tc_pair_supports(M, N, K)) {
         return fail(LBL_ERR_UNSUPPORTED, "paired tensor-core GEMM cannot serve M=%lld N=%lld K=%lld (needs N %% 256 == 0, K %% 256 == 0)", (long long)M, (long long)N, (long long)K);
       }
-      err = lbl::launch_gemm_tc_pair(prob, info.status_word, cu_stream);
+      err = lbl::launch_gemm_tc_pair(prob, info.status_word, cu_stream, (flags & LBL_FLAG_PDL) != 0,
+                                     (flags & LBL_FLAG_INDEPENDENT) != 0);
       break;
     }
     case LBL_PATH_GEMM_WT: {

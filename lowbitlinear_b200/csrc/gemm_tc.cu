@@ -28,7 +28,9 @@
 // exact policy).
 // Every wait on an mbarrier is bounded; a timeout sets the device status word and the CTA drains.
 // With programmatic dependent launch the set-up and the weights of the first stages overlap the
-// previous kernel in the stream; the X loads and the outputs wait for it.
+// previous kernel in the stream; the X loads and the outputs wait for it -- unless the caller
+// declares the call independent of that kernel (LBL_FLAG_INDEPENDENT), in which case nothing waits
+// and this kernel's CTAs fill the SMs that the last, partial wave of the previous one leaves idle.
 // Shapes: N % 256 == 0 and K % 256 == 0; any M >= 1.  No cluster launch, no multicast.
 #include "kernels.h"
 #include "tc_common.cuh"
@@ -66,6 +68,7 @@ struct GemmParams {
   __half* y;
   int M, N, K;
   int m_tiles;
+  int wait_previous;  // programmatic dependent launch: wait for the previous kernel before touching X and Y
   int* status;
 };
 
@@ -117,7 +120,7 @@ __global__ void __launch_bounds__(kThreads, 1)
   if (warp == 0) {
     // ------------------------------- TMA producer (X blocks) ---------------------------------
     if (lane == 0) {
-      pdl_wait_for_previous_kernel();
+      if (p.wait_previous) pdl_wait_for_previous_kernel();
       for (int kb = 0; kb < k_blocks; ++kb) {
         const int s = kb % kStages;
         const int round = kb / kStages;
@@ -169,7 +172,7 @@ __global__ void __launch_bounds__(kThreads, 1)
     // ------------------------------- epilogue ---------------------------------------------------
     const bool ok = mbar_wait_bounded(&bars->acc_full, 0, abort_flag, p.status, kStatusGemmWait + 5);
     tc_fence_after_sync();
-    pdl_wait_for_previous_kernel();  // before the first write to Y
+    if (p.wait_previous) pdl_wait_for_previous_kernel();  // before the first write to Y
     const int quarter = warp & 3;        // TMEM lanes this warp may read
     const int h = ((warp - 2) >> 2) & 1;  // accumulator handled by this warp
     const int column_half = (warp - 2) >> 3;  // two warps share a quarter of an accumulator
@@ -221,7 +224,7 @@ bool gemm_tc_supports(int64_t M, int64_t N, int64_t K) {
          N <= (1 << 24) && K <= (1 << 24) && (N / kBN) * ((M + kBM - 1) / kBM) <= 0x7fffffffLL;
 }
 
-cudaError_t launch_gemm_tc(const Problem& p, int* status_word, cudaStream_t stream, bool pdl) {
+cudaError_t launch_gemm_tc(const Problem& p, int* status_word, cudaStream_t stream, bool pdl, bool independent) {
   CUtensorMap tmap;
   const uint64_t dims[2] = {static_cast<uint64_t>(p.K), static_cast<uint64_t>(p.M)};
   const uint64_t strides[1] = {static_cast<uint64_t>(p.K) * sizeof(__half)};
@@ -252,6 +255,7 @@ cudaError_t launch_gemm_tc(const Problem& p, int* status_word, cudaStream_t stre
   gp.K = static_cast<int>(p.K);
   gp.m_tiles = static_cast<int>((p.M + kBM - 1) / kBM);
   gp.status = status_word;
+  gp.wait_previous = independent ? 0 : 1;
   const unsigned grid = static_cast<unsigned>((p.N / kBN) * gp.m_tiles);
   cudaLaunchConfig_t cfg = {};
   cfg.gridDim = dim3(grid);

@@ -83,6 +83,7 @@ struct PairParams {
   __half* y;
   int M, N, K;
   int m_tiles;  // ceil(M / 512)
+  int wait_previous;  // programmatic dependent launch: wait for the previous kernel before touching X and Y
   int* status;
 };
 
@@ -202,10 +203,16 @@ __global__ void __launch_bounds__(kThreads, 1)
   tc_fence_after_sync();
   const uint32_t tmem_base = *reinterpret_cast<volatile uint32_t*>(&bars->tmem_base);
   const uint32_t peer_ready_leader = map_to_cta(smem_addr(&bars->peer_ready[0]), 0);
+  // Programmatic dependent launch (no-ops without it): the next kernel in the stream may start as
+  // soon as every CTA of this one is running.  Weights never depend on the previous kernel; X and Y
+  // wait for it unless the caller has declared this call independent of it, and then this kernel's
+  // pairs fill the SMs that the previous kernel's last, partial wave leaves idle.
+  pdl_allow_next_kernel();
 
   if (warp == 0) {
     // ------------------------------- TMA producer (this CTA's X rows) ---------------------------
     if (lane == 0) {
+      if (p.wait_previous) pdl_wait_for_previous_kernel();
       for (int kb = 0; kb < k_blocks; ++kb) {
         const int s = kb % kStagesA;
         const int round = kb / kStagesA;
@@ -276,6 +283,7 @@ __global__ void __launch_bounds__(kThreads, 1)
     // ------------------------------- epilogue ---------------------------------------------------
     const bool ok = mbar_wait_bounded(&bars->acc_full, 0, abort_flag, p.status, kStatusPairWait + 5);
     tc_fence_after_sync();
+    if (p.wait_previous) pdl_wait_for_previous_kernel();  // before the first write to Y
     const int quarter = warp & 3;               // TMEM lanes this warp may read
     const int g = ((warp - 2) >> 2) & 1;        // token group (accumulator) handled by this warp
     const int column_part = (warp - 2) >> 3;    // with sixteen warps two share a quarter of an accumulator
@@ -331,7 +339,7 @@ bool gemm_tc_pair_supports(int64_t M, int64_t N, int64_t K) {
          (N / kNPair) * ((M + kTokensPair - 1) / kTokensPair) <= 0x3fffffffLL;
 }
 
-cudaError_t launch_gemm_tc_pair(const Problem& p, int* status_word, cudaStream_t stream) {
+cudaError_t launch_gemm_tc_pair(const Problem& p, int* status_word, cudaStream_t stream, bool pdl, bool independent) {
   CUtensorMap tmap;
   const uint64_t dims[2] = {static_cast<uint64_t>(p.K), static_cast<uint64_t>(p.M)};
   const uint64_t strides[1] = {static_cast<uint64_t>(p.K) * sizeof(__half)};
@@ -359,19 +367,22 @@ cudaError_t launch_gemm_tc_pair(const Problem& p, int* status_word, cudaStream_t
   pp.K = static_cast<int>(p.K);
   pp.m_tiles = static_cast<int>((p.M + kTokensPair - 1) / kTokensPair);
   pp.status = status_word;
+  pp.wait_previous = independent ? 0 : 1;
   const unsigned pairs = static_cast<unsigned>((p.N / kNPair) * pp.m_tiles);
   cudaLaunchConfig_t cfg = {};
   cfg.gridDim = dim3(2 * pairs);
   cfg.blockDim = dim3(kThreads);
   cfg.dynamicSmemBytes = kSmemBytes;
   cfg.stream = stream;
-  cudaLaunchAttribute attr[1];
+  cudaLaunchAttribute attr[2];
   attr[0].id = cudaLaunchAttributeClusterDimension;
   attr[0].val.clusterDim.x = 2;
   attr[0].val.clusterDim.y = 1;
   attr[0].val.clusterDim.z = 1;
+  attr[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[1].val.programmaticStreamSerializationAllowed = 1;
   cfg.attrs = attr;
-  cfg.numAttrs = 1;
+  cfg.numAttrs = pdl ? 2 : 1;
   return cudaLaunchKernelEx(&cfg, w4a16_gemm_tc_pair_kernel, tmap, pp);
 }
 

@@ -125,7 +125,8 @@ cudaError_t launch_gemv_grouped(const GroupPlan* plan, bool pdl, cudaStream_t st
 
 // ----- TMA + tcgen05 GEMM (gemm_tc.cu) ---------------------------------------------------------
 bool gemm_tc_supports(int64_t M, int64_t N, int64_t K);
-cudaError_t launch_gemm_tc(const Problem& p, int* status_word, cudaStream_t stream, bool pdl);
+// `independent`: with `pdl`, do not wait for the previous kernel in the stream at all.
+cudaError_t launch_gemm_tc(const Problem& p, int* status_word, cudaStream_t stream, bool pdl, bool independent);
 
 // ----- tcgen05 GEMM for M <= 128, weights on the M side of the MMA (gemm_tc_small.cu) ----------
 bool gemm_tc_small_supports(int64_t M, int64_t N, int64_t K);
@@ -138,7 +139,7 @@ cudaError_t launch_gemm_tc_small(const Problem& p, int* status_word, cudaStream_
 
 // ----- TMA + tcgen05 GEMM on pairs of CTAs, cta_group::2 (gemm_tc2.cu) ---------------------------
 bool gemm_tc_pair_supports(int64_t M, int64_t N, int64_t K);
-cudaError_t launch_gemm_tc_pair(const Problem& p, int* status_word, cudaStream_t stream);
+cudaError_t launch_gemm_tc_pair(const Problem& p, int* status_word, cudaStream_t stream, bool pdl, bool independent);
 
 // ----- tcgen05 GEMM with the weights passed through tensor memory (gemm_wt.cu) ------------------
 bool gemm_wt_supports(int64_t M, int64_t N, int64_t K);

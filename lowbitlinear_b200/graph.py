@@ -94,6 +94,9 @@ class GraphedLinears:
         # resources a collective is waiting for, so it is used only without NCCL in the graph.
         nccl_in_graph = world > 1 and not grouped
         _ops.set_programmatic_dependent_launch(programmatic_dependent_launch and not nccl_in_graph)
+        # The layers of a runner are independent of each other (own activations, own outputs), so a
+        # launch need not wait for the one before it: the tensor-core GEMMs fill each other's tails.
+        _ops.set_independent_launches(programmatic_dependent_launch and not nccl_in_graph)
         try:
             self.stream.wait_stream(torch.cuda.current_stream(device))
             with torch.cuda.stream(self.stream):
