@@ -117,6 +117,10 @@ int select_path(int64_t M, int64_t N, int64_t K, int op, int sm_count) {
   if (M >= kTcSmallMinM && lbl::gemm_tc_small_supports(M, N, K) && (!wide || M <= 32 || !tc_ok)) {
     return LBL_PATH_GEMM_TC_SMALL;
   }
+  // A long K whose activations do not fit the streaming kernel's operand budget is split along K
+  // there (ordered fix-up); from six rows on the small tensor-core GEMM is faster (Down, M = 8:
+  // 29 against 36 us).
+  if (M >= 6 && M * K * 2 > 65536 && !wide && lbl::gemm_tc_small_supports(M, N, K)) return LBL_PATH_GEMM_TC_SMALL;
   // More than 128 rows of activations on a shape whose 256 x 256 tiles would leave most SMs idle
   // (less than half a wave: small N, a tensor-parallel shard): the tensor-memory GEMM cuts K into
   // slices until the SMs are busy.  Also the only tensor-core kernel for N % 256 == 128.

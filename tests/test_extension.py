@@ -131,7 +131,8 @@ def test_dispatcher_choices_and_scratch_sizes():
         assert name(1, 4096, 4096) == "gemv"
         assert name(1, 4096, 12288) == "gemv"
         assert name(1, 512, 4096) == "gemv_splitk"     # a tensor-parallel shard: 32 row tiles
-        assert name(8, 4096, 12288) == "gemv_splitk"   # activations of one segment must fit on chip
+        assert name(4, 4096, 12288) == "gemv_splitk"   # activations of one segment must fit on chip
+        assert name(8, 4096, 12288) == "gemm_tc_small" # ... and from six rows on the tensor cores are faster
         # Prefill shapes go to the tensor cores; ragged shapes to the masked kernel.
         assert name(2048, 24576, 4096) == "gemm_tc_pair"   # pairs of CTAs share the dequantised weights
         assert name(256, 24576, 4096) == "gemm_tc"

@@ -258,7 +258,11 @@ def test_crossover_shapes_meet_the_benchmark_tolerance_on_every_path(name, m, cu
         assert_north_star_parity(y[:, rows], oracle_rows)
     picked = _ops.PATH_NAMES[_ops.select_path(m, n, k)]
     picked = "gemv" if picked == "gemv_splitk" else picked
-    assert torch.equal(results["forward"], results[picked])
+    if picked == "gemv" and _ops.select_path(m, n, k) == _ops.PATH_GEMV_SPLITK:
+        # Forced and automatic plans may split K differently: same value up to the last bit.
+        torch.testing.assert_close(results["forward"], results[picked], atol=ATOL, rtol=RTOL)
+    else:
+        assert torch.equal(results["forward"], results[picked])
 
 
 @pytest.mark.parametrize("name", ["gate_up", "down"])
