@@ -17,7 +17,8 @@ are independent of each other.  For decode (``m <= 2``) the whole set is ONE per
 
 Tensor parallel: give every rank its shards, flag the K-split (row-parallel) ones in ``reduce``
 and pass the ranks' ``PeerExchange``; the flagged outputs are summed over the ranks by the
-group's second kernel (decode) or by an NCCL all-reduce captured in the graph (larger ``m``).
+group's second kernel (decode) or by NCCL all-reduces captured in the graph (larger ``m``), issued
+asynchronously so that they overlap the launches that follow.
 """
 import torch
 
@@ -90,13 +91,14 @@ class GraphedLinears:
         self.stream = torch.cuda.Stream(device=device)
         self.graph = torch.cuda.CUDAGraph()
         previous = _ops._flags
-        # Between launches that alternate with NCCL kernels a dependent launch could hold SM
-        # resources a collective is waiting for, so it is used only without NCCL in the graph.
-        nccl_in_graph = world > 1 and not grouped
-        _ops.set_programmatic_dependent_launch(programmatic_dependent_launch and not nccl_in_graph)
+        # Without the grouped launch the K-split outputs are summed by NCCL.  The all-reduces are
+        # issued asynchronously (NCCL's own stream) and waited for at the end of the step, so they
+        # overlap the launches that follow; programmatic dependent launch stays on between the
+        # library's own kernels.
+        _ops.set_programmatic_dependent_launch(programmatic_dependent_launch)
         # The layers of a runner are independent of each other (own activations, own outputs), so a
         # launch need not wait for the one before it: the tensor-core GEMMs fill each other's tails.
-        _ops.set_independent_launches(programmatic_dependent_launch and not nccl_in_graph)
+        _ops.set_independent_launches(programmatic_dependent_launch)
         try:
             self.stream.wait_stream(torch.cuda.current_stream(device))
             with torch.cuda.stream(self.stream):
@@ -112,12 +114,15 @@ class GraphedLinears:
         if self.grouped:
             self.linear_group.run()
             return
+        pending = []
         for layer, x, y, reduce in zip(self.layers, self.xs, self.ys, self.reduce):
             _ops.linear_out(x, layer.packed_weight, layer.scales, layer.zeros, y, workspace=self.scratch)
             if reduce and self.world > 1:
                 import torch.distributed as dist
 
-                dist.all_reduce(y, group=self.process_group)
+                pending.append(dist.all_reduce(y, group=self.process_group, async_op=True))
+        for work in pending:
+            work.wait()
 
     def replay(self):
         """Replay on the current stream with whatever ``x_flat`` holds; results in ``y_flat``."""
