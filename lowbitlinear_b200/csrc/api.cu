@@ -208,6 +208,13 @@ int run_linear(const void* X, const int32_t* packed_w, const float* scales, cons
       path = LBL_PATH_GENERIC;
     }
   }
+  // Calls declared independent of their neighbours overlap in time: the CTAs of the next call fill
+  // the SMs this one leaves idle, so a tile count far below a wave is no loss, and the paired
+  // kernel (no scratch, never waits) beats cutting K into slices (scratch, waits for its neighbours).
+  if (!forced && path == LBL_PATH_GEMM_WT && (flags & LBL_FLAG_PDL) != 0 && (flags & LBL_FLAG_INDEPENDENT) != 0 &&
+      M >= 384 && lbl::gemm_tc_pair_supports(M, N, K)) {
+    path = LBL_PATH_GEMM_TC_PAIR;
+  }
   // The fast kernels use 16-byte vector accesses and bulk copies on every operand.
   const bool all_aligned = aligned16(X) && aligned16(packed_w) && aligned16(scales) &&
                            aligned16(zeros) && aligned16(Y);
