@@ -675,7 +675,12 @@ def run_prefill(ctx, layers, reference):
     m = PREFILL_M
     reduce = [name == "down" for name, _ in layers]
     modules = [layer for _, layer in layers]
-    runner = GraphedLinears(modules, m=m, reduce=reduce)
+    gemm_exchange = None
+    if world > 1 and args.allreduce == "fused":
+        from lowbitlinear_b200.tensor_parallel import PeerExchange
+        gemm_exchange = PeerExchange.for_gemm(m, SHAPES[3][1], device)
+    runner = GraphedLinears(modules, m=m, reduce=reduce, gemm_exchange=gemm_exchange)
+    fused = gemm_exchange is not None and any(runner.fused)
     fill_activations(runner, layers, m, device, ctx.rank, world, None)
     # Layer 0: rows 0..3 of every activation are the CPU reference's M = 1 activations, so the
     # reference outputs of the decode leg check the GEMM as well.
@@ -697,6 +702,17 @@ def run_prefill(ctx, layers, reference):
             cols = n // world
             want = want[:, ctx.rank * cols:(ctx.rank + 1) * cols]
         parity[name] = ctx.max_over_ranks(check_parity(got, want, f"layer 0 {name} (M={m}, row 0) vs the CPU reference"))
+    if world > 1:
+        # The all-reduced Down output (all 2048 rows) must be the same bits on every rank.
+        mine = runner.ys[3].clone()
+        theirs = mine.clone()
+        ctx.dist.broadcast(theirs, src=0)
+        same = torch.tensor([1.0 if torch.equal(mine, theirs) else 0.0], device=device)
+        ctx.dist.all_reduce(same, op=ctx.dist.ReduceOp.MIN)
+        parity["down_bit_identical_across_ranks"] = bool(same.item() == 1.0)
+        if not parity["down_bit_identical_across_ranks"]:
+            raise SystemExit("prefill: the all-reduced Down output differs between ranks")
+        del mine, theirs
     for i in (6, 75):  # whole outputs of two other linears against an FP32 evaluation on the GPU
         name, layer = layers[i]
         if world > 1 and name == "down":
@@ -737,6 +753,10 @@ def run_prefill(ctx, layers, reference):
             dev_x.copy_(host_x, non_blocking=True)
             for j in range(chunk):
                 name, layer = layers[c * chunk + j]
+                if fused and name == "down":
+                    _ops.gemm_allreduce(x_views[j], layer.packed_weight, layer.scales, layer.zeros, gemm_exchange,
+                                        out=y_views[j])
+                    continue
                 _ops.linear_out(x_views[j], layer.packed_weight, layer.scales, layer.zeros, y_views[j],
                                 workspace=scratch)
                 if world > 1 and name == "down":
@@ -767,9 +787,16 @@ def run_prefill(ctx, layers, reference):
                      "h2d_bytes_per_step": int(x_elems * 2 * LAYERS), "d2h_bytes_per_step": int(y_elems * 2 * LAYERS),
                      "api": "lowbitlinear_b200._ops.linear_out per linear, eager, one layer's pinned host activations "
                             "in and host outputs out at a time"},
-             "gpu_launches": len(layers) * args.steps,
-             "launch": "CUDA graph of 144 launches" + ("" if world == 1 else " with 36 NCCL all-reduces"),
+             "gpu_launches": (len(layers) + (2 * LAYERS if fused else 0)) * args.steps,
+             "launch": "CUDA graph of 144 launches" + (
+                 "" if world == 1 else
+                 " (Down: GEMM whose epilogue scatters its partial tiles to the owner ranks over NVLink) + 2 x 36 "
+                 "reduce / gather kernels over peer memory on a side stream" if fused else
+                 " with 36 NCCL all-reduces, issued asynchronously"),
              "parity": {"rel_l2_vs_cpu_reference": parity, "tolerance": TOLERANCE}}
+    if gemm_exchange is not None:
+        del runner
+        gemm_exchange.close()
     return block
 
 
@@ -997,6 +1024,8 @@ def main():
     parser.add_argument("--impl", choices=("ours", "reference", "reference_gpu"), default="ours")
     parser.add_argument("--workload", choices=("stack", "decode", "prefill", "crossover", "prefill_sweep"),
                         default="stack")
+    parser.add_argument("--allreduce", choices=("fused", "nccl"), default="fused",
+                        help="prefill at N > 1: all-reduce of the Down output fused into the GEMM (peer memory) or NCCL")
     parser.add_argument("--emit", default=None, help=argparse.SUPPRESS)
     args = parser.parse_args()
     if args.impl == "reference":

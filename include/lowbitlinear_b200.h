@@ -163,6 +163,43 @@ int lbl_w4a16_gemv_allreduce(const void* x, const int32_t* packed_w, const float
                              void* workspace, size_t workspace_bytes, unsigned flags, int device,
                              void* stream);
 
+/* ---- K-split GEMM with the all-reduce fused into it (large M, tensor parallel) ----------------
+ * The reference has no multi-GPU path; this is the large-M counterpart of
+ * lbl_w4a16_gemv_allreduce.  Rank r holds columns [r K / world, (r + 1) K / world) of the weight
+ * (x, packed_w, scales, zeros are the rank's shard; K is the shard's K).  Rank o owns the output
+ * columns [o N / world, (o + 1) N / world).
+ *   lbl_w4a16_gemm_scatter            the tcgen05 GEMM on CTA pairs; each finished 512 x 256 tile of
+ *                                     partial outputs is stored, FP16, straight into the exchange
+ *                                     buffer of the rank that owns its columns (NVLink peer stores
+ *                                     from the epilogue, tile by tile while the GEMM runs).
+ *   lbl_peer_gemm_allreduce_finish    two launches: (1) flags to and from every peer, then each
+ *                                     rank adds the `world` partials of its own columns in rank
+ *                                     order (FP32 sums, one rounding to FP16) into y and into its
+ *                                     result block; (2) flags again, then each rank copies the
+ *                                     peers' result blocks into y with vector loads over NVLink.
+ *                                     Every rank ends with the same bits in y[M, N].
+ *   lbl_w4a16_gemm_allreduce          both, on one stream.
+ * Exchange buffers: lbl_peer_buffer_create(lbl_peer_gemm_buffer_bytes(M, N, world)), exported and
+ * opened like the decode buffers; buffers[r] is rank r's buffer as mapped here, buffer_bytes the
+ * size all of them have.  One all-reduce per set of buffers at a time: the next scatter into them
+ * must be ordered after this rank's finish (same stream, or an event when finish runs on a side
+ * stream so that other GEMMs overlap it).  All ranks make the same sequence of calls.  Needs
+ * N % (256 * world) == 0 and K % 256 == 0; LBL_FLAG_PDL / LBL_FLAG_INDEPENDENT apply to the GEMM
+ * launch.  Waits for peers are bounded (about 2 s): on expiry y is filled with NaN and
+ * lbl_device_status reports 110. */
+size_t lbl_peer_gemm_buffer_bytes(int64_t M, int64_t N, int world);
+int lbl_w4a16_gemm_scatter(const void* x, const int32_t* packed_w, const float* scales,
+                           const int32_t* zeros, int64_t M, int64_t N, int64_t K, int rank, int world,
+                           void* const* buffers, size_t buffer_bytes, unsigned flags, int device,
+                           void* stream);
+int lbl_peer_gemm_allreduce_finish(void* y, int64_t M, int64_t N, int rank, int world,
+                                   void* const* buffers, size_t buffer_bytes, int device,
+                                   void* stream);
+int lbl_w4a16_gemm_allreduce(const void* x, const int32_t* packed_w, const float* scales,
+                             const int32_t* zeros, void* y, int64_t M, int64_t N, int64_t K, int rank,
+                             int world, void* const* buffers, size_t buffer_bytes, unsigned flags,
+                             int device, void* stream);
+
 /* ---- Grouped decode GEMV: many independent problems, one launch ------------------------------
  * The reference launches one kernel per linear (csrc/w4a16_gemv_warp_vec.cu:171-187); at decode
  * sizes the fixed cost of a launch rivals the time its weights need to cross the memory bus.  A

@@ -93,6 +93,15 @@ def bind(path):
     lib.lbl_w4a16_gemv_allreduce.restype = i32
     lib.lbl_w4a16_gemv_allreduce.argtypes = [p, p, p, p, p, i64, i64, i32, i32, i32, ctypes.POINTER(p), i64,
                                              p, sz, u32, i32, p]
+    lib.lbl_peer_gemm_buffer_bytes.restype = sz
+    lib.lbl_peer_gemm_buffer_bytes.argtypes = [i64, i64, i32]
+    lib.lbl_w4a16_gemm_scatter.restype = i32
+    lib.lbl_w4a16_gemm_scatter.argtypes = [p, p, p, p, i64, i64, i64, i32, i32, ctypes.POINTER(p), sz, u32, i32, p]
+    lib.lbl_peer_gemm_allreduce_finish.restype = i32
+    lib.lbl_peer_gemm_allreduce_finish.argtypes = [p, i64, i64, i32, i32, ctypes.POINTER(p), sz, i32, p]
+    lib.lbl_w4a16_gemm_allreduce.restype = i32
+    lib.lbl_w4a16_gemm_allreduce.argtypes = [p, p, p, p, p, i64, i64, i64, i32, i32, ctypes.POINTER(p), sz, u32,
+                                             i32, p]
     lib.lbl_w4a16_quantize.restype = i32
     lib.lbl_w4a16_quantize.argtypes = [p, i32, i64, i64, i32, p, p, p, i32, p]
     lib.lbl_w4a16_dequantize.restype = i32
@@ -344,6 +353,38 @@ def gemv_allreduce(x, packed_w, scales, zeros, exchange):
              x.data_ptr(), packed_w.data_ptr(), scales.data_ptr(), zeros.data_ptr(), y.data_ptr(), n, k,
              64, exchange.rank, exchange.world, exchange.pointers, exchange.capacity_n, ws, ws_bytes,
              _flags, x.device.index, stream))
+    return y
+
+
+def gemm_scatter(x, packed_w, scales, zeros, exchange, flags=None):
+    """First half of the K-split GEMM with fused all-reduce: ``x`` is this rank's ``[M, K/g]``
+    slice of the activation, the weights its column slice.  Launches the tcgen05 GEMM on the
+    current stream; each finished tile of partial outputs is stored from the epilogue straight
+    into the exchange buffer of the rank that owns its columns.  ``exchange`` is a
+    ``tensor_parallel.PeerExchange.for_gemm``; follow with ``gemm_allreduce_finish``."""
+    m, k = x.shape
+    n = packed_w.size(0)
+    _check(_lib.lbl_w4a16_gemm_scatter(
+        x.data_ptr(), packed_w.data_ptr(), scales.data_ptr(), zeros.data_ptr(), m, n, k, exchange.rank,
+        exchange.world, exchange.pointers, exchange.bytes, _flags if flags is None else flags, x.device.index,
+        _raw_stream(x.device)))
+
+
+def gemm_allreduce_finish(y, exchange):
+    """Second half: on the current stream, add the ranks' partial outputs of this rank's columns
+    and gather the other ranks' columns into ``y`` ``[M, N]`` FP16 (identical on every rank).  May
+    run on another stream than the GEMM if an event orders it after the GEMM, and the next
+    ``gemm_scatter`` into the same exchange after it."""
+    m, n = y.shape
+    _check(_lib.lbl_peer_gemm_allreduce_finish(y.data_ptr(), m, n, exchange.rank, exchange.world, exchange.pointers,
+                                               exchange.bytes, y.device.index, _raw_stream(y.device)))
+
+
+def gemm_allreduce(x, packed_w, scales, zeros, exchange, out=None):
+    """K-split GEMM and all-reduce on the current stream; returns the full ``[M, N]``."""
+    y = out if out is not None else torch.empty((x.size(0), packed_w.size(0)), dtype=torch.float16, device=x.device)
+    gemm_scatter(x, packed_w, scales, zeros, exchange)
+    gemm_allreduce_finish(y, exchange)
     return y
 
 

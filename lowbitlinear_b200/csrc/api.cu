@@ -659,6 +659,95 @@ int lbl_w4a16_gemv_allreduce(const void* x, const int32_t* packed_w, const float
 }
 
 // ---------------------------------------------------------------------------------------------
+// K-split GEMM with a two-shot all-reduce over peer memory (large M).
+// ---------------------------------------------------------------------------------------------
+size_t lbl_peer_gemm_buffer_bytes(int64_t M, int64_t N, int world) {
+  if (M <= 0 || N <= 0 || world < 1 || world > 8 || N % world != 0) return 0;
+  return lbl::peer_gemm_buffer_bytes(M, N, world);
+}
+
+static int check_gemm_exchange(int64_t M, int64_t N, int rank, int world, void* const* buffers, size_t buffer_bytes) {
+  if (world < 2 || world > 8 || rank < 0 || rank >= world || buffers == nullptr) return fail(LBL_ERR_INVALID, "bad rank/world/buffers");
+  if (M <= 0 || N <= 0 || M > 0x7fffffffLL || N > 0x7fffffffLL) return fail(LBL_ERR_INVALID, "bad shape M=%lld N=%lld", (long long)M, (long long)N);
+  if (N % (256 * world) != 0) {
+    return fail(LBL_ERR_UNSUPPORTED, "the GEMM all-reduce needs N %% (256 * world) == 0 (N=%lld, world=%d)", (long long)N, world);
+  }
+  const size_t need = lbl::peer_gemm_buffer_bytes(M, N, world);
+  if (buffer_bytes < need) return fail(LBL_ERR_WORKSPACE, "exchange buffers hold %zu bytes, M=%lld N=%lld needs %zu", buffer_bytes, (long long)M, (long long)N, need);
+  for (int r = 0; r < world; ++r) {
+    if (buffers[r] == nullptr || !aligned16(buffers[r])) return fail(LBL_ERR_INVALID, "exchange buffer of rank %d is null or misaligned", r);
+  }
+  return LBL_OK;
+}
+
+int lbl_w4a16_gemm_scatter(const void* x, const int32_t* packed_w, const float* scales, const int32_t* zeros,
+                           int64_t M, int64_t N, int64_t K, int rank, int world, void* const* buffers,
+                           size_t buffer_bytes, unsigned flags, int device, void* stream) {
+  int rc = check_gemm_exchange(M, N, rank, world, buffers, buffer_bytes);
+  if (rc != LBL_OK) return rc;
+  if (!lbl::gemm_tc_pair_supports(M, N, K)) {
+    return fail(LBL_ERR_UNSUPPORTED, "the scattering GEMM needs N %% 256 == 0 and K %% 256 == 0 (N=%lld K=%lld)", (long long)N, (long long)K);
+  }
+  if (x == nullptr || packed_w == nullptr || scales == nullptr || zeros == nullptr) return fail(LBL_ERR_INVALID, "null tensor pointer");
+  if (!aligned16(x) || !aligned16(packed_w) || !aligned16(scales) || !aligned16(zeros)) return fail(LBL_ERR_INVALID, "all tensors must be 16-byte aligned");
+  DeviceScope scope(device);
+  if (!scope.ok()) return fail(LBL_ERR_CUDA, "cannot make device %d current", device);
+  DeviceInfo info;
+  rc = device_info(device, &info);
+  if (rc != LBL_OK) return rc;
+  lbl::Problem prob;
+  prob.x = static_cast<const __half*>(x);
+  prob.packed = reinterpret_cast<const uint32_t*>(packed_w);
+  prob.scales = scales;
+  prob.zeros = zeros;
+  prob.y = nullptr;
+  prob.M = M;
+  prob.N = N;
+  prob.K = K;
+  lbl::PairScatter scatter;
+  scatter.world = world;
+  const size_t slice_bytes = static_cast<size_t>(M) * (N / world) * sizeof(__half);
+  for (int r = 0; r < 8; ++r) {
+    scatter.slot[r] = r < world ? reinterpret_cast<__half*>(static_cast<unsigned char*>(buffers[r]) + lbl::kPeerBufferHeaderBytes + rank * slice_bytes) : nullptr;
+  }
+  const bool pdl = (flags & LBL_FLAG_PDL) != 0;
+  const cudaError_t err = lbl::launch_gemm_tc_pair(prob, info.status_word, static_cast<cudaStream_t>(stream), pdl,
+                                                   pdl && (flags & LBL_FLAG_INDEPENDENT) != 0, &scatter);
+  if (err != cudaSuccess) return fail_cuda(err, "kernel launch");
+  return LBL_OK;
+}
+
+int lbl_peer_gemm_allreduce_finish(void* y, int64_t M, int64_t N, int rank, int world, void* const* buffers,
+                                   size_t buffer_bytes, int device, void* stream) {
+  const int rc0 = check_gemm_exchange(M, N, rank, world, buffers, buffer_bytes);
+  if (rc0 != LBL_OK) return rc0;
+  if (y == nullptr || !aligned16(y)) return fail(LBL_ERR_INVALID, "y is null or not 16-byte aligned");
+  DeviceScope scope(device);
+  if (!scope.ok()) return fail(LBL_ERR_CUDA, "cannot make device %d current", device);
+  DeviceInfo info;
+  const int rc = device_info(device, &info);
+  if (rc != LBL_OK) return rc;
+  lbl::PeerReduce exchange;
+  exchange.rank = rank;
+  exchange.world = world;
+  exchange.capacity_n = 0;
+  for (int r = 0; r < 8; ++r) exchange.buffers[r] = r < world ? buffers[r] : nullptr;
+  const cudaError_t err = lbl::launch_peer_slice_allreduce(exchange, static_cast<__half*>(y), M, N, info.sm_count,
+                                                           info.status_word, static_cast<cudaStream_t>(stream));
+  if (err != cudaSuccess) return fail_cuda(err, "kernel launch");
+  return LBL_OK;
+}
+
+int lbl_w4a16_gemm_allreduce(const void* x, const int32_t* packed_w, const float* scales, const int32_t* zeros,
+                             void* y, int64_t M, int64_t N, int64_t K, int rank, int world, void* const* buffers,
+                             size_t buffer_bytes, unsigned flags, int device, void* stream) {
+  const int rc = lbl_w4a16_gemm_scatter(x, packed_w, scales, zeros, M, N, K, rank, world, buffers, buffer_bytes, flags,
+                                        device, stream);
+  if (rc != LBL_OK) return rc;
+  return lbl_peer_gemm_allreduce_finish(y, M, N, rank, world, buffers, buffer_bytes, device, stream);
+}
+
+// ---------------------------------------------------------------------------------------------
 // Grouped decode GEMV: a list of independent problems in one persistent launch.
 // ---------------------------------------------------------------------------------------------
 struct lbl_w4a16_group {

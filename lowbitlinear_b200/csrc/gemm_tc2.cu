@@ -64,6 +64,7 @@ constexpr int kSmemBytes = kStagesA * kStageBytesA + kStagesB * kStageBytesB + k
 constexpr int kStatusPairWait = 500;
 
 constexpr int kRelaySlots = 4;
+constexpr int kMaxScatterRanks = 8;
 struct Barriers {
   uint64_t a_full[kStagesA];   // this CTA's X blocks have landed
   uint64_t a_empty[kStagesA];  // the MMAs have read the X stage (cluster-wide commit)
@@ -85,6 +86,11 @@ struct PairParams {
   int m_tiles;  // ceil(M / 512)
   int wait_previous;  // programmatic dependent launch: wait for the previous kernel before touching X and Y
   int* status;
+  // Tensor-parallel K split: instead of y, the tile goes to the rank that owns its columns --
+  // scatter[o] is this rank's slot [M, owner_cols] in the exchange buffer of rank o (peer memory
+  // for o != this rank), written with plain 16-byte stores over NVLink as each tile finishes.
+  __half* scatter[kMaxScatterRanks];
+  int owner_cols;  // 0: no scatter
 };
 
 constexpr uint32_t kInstrDescPair = instr_desc_f16(256, 256);
@@ -290,7 +296,13 @@ __global__ void __launch_bounds__(kThreads, 1)
     constexpr int kColumnParts = kDequantWarps / 8;
     if (ok) {
       const int m = m0 + g * 256 + quarter * 32 + lane;
-      __half* out_row = p.y + static_cast<size_t>(m < p.M ? m : 0) * p.N + n0;
+      __half* out_row;
+      if (p.owner_cols == 0) {
+        out_row = p.y + static_cast<size_t>(m < p.M ? m : 0) * p.N + n0;
+      } else {
+        const int owner = n0 / p.owner_cols;
+        out_row = p.scatter[owner] + static_cast<size_t>(m < p.M ? m : 0) * p.owner_cols + (n0 - owner * p.owner_cols);
+      }
       const uint32_t taddr = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) + g * 256;
       for (int c0 = column_part * (kNPair / kColumnParts); c0 < (column_part + 1) * (kNPair / kColumnParts); c0 += 32) {
         uint32_t v[32];
@@ -312,6 +324,8 @@ __global__ void __launch_bounds__(kThreads, 1)
           }
         }
       }
+      // Tiles sent to a peer: order them before whatever this GPU tells that peer afterwards.
+      if (p.owner_cols != 0) __threadfence_system();
     }
   }
 
@@ -339,7 +353,14 @@ bool gemm_tc_pair_supports(int64_t M, int64_t N, int64_t K) {
          (N / kNPair) * ((M + kTokensPair - 1) / kTokensPair) <= 0x3fffffffLL;
 }
 
-cudaError_t launch_gemm_tc_pair(const Problem& p, int* status_word, cudaStream_t stream, bool pdl, bool independent) {
+cudaError_t launch_gemm_tc_pair(const Problem& p, int* status_word, cudaStream_t stream, bool pdl, bool independent,
+                                const PairScatter* scatter) {
+  if (scatter != nullptr) {
+    if (scatter->world < 2 || scatter->world > kMaxScatterRanks || p.N % scatter->world != 0 ||
+        (p.N / scatter->world) % kNPair != 0) {
+      return cudaErrorInvalidValue;
+    }
+  }
   CUtensorMap tmap;
   const uint64_t dims[2] = {static_cast<uint64_t>(p.K), static_cast<uint64_t>(p.M)};
   const uint64_t strides[1] = {static_cast<uint64_t>(p.K) * sizeof(__half)};
@@ -368,6 +389,12 @@ cudaError_t launch_gemm_tc_pair(const Problem& p, int* status_word, cudaStream_t
   pp.m_tiles = static_cast<int>((p.M + kTokensPair - 1) / kTokensPair);
   pp.status = status_word;
   pp.wait_previous = independent ? 0 : 1;
+  pp.owner_cols = 0;
+  for (int r = 0; r < kMaxScatterRanks; ++r) pp.scatter[r] = nullptr;
+  if (scatter != nullptr) {
+    pp.owner_cols = static_cast<int>(p.N / scatter->world);
+    for (int r = 0; r < scatter->world; ++r) pp.scatter[r] = scatter->slot[r];
+  }
   const unsigned pairs = static_cast<unsigned>((p.N / kNPair) * pp.m_tiles);
   cudaLaunchConfig_t cfg = {};
   cfg.gridDim = dim3(2 * pairs);

@@ -102,6 +102,17 @@ struct PeerReduceLaunch {
 // its own device.  Advances the exchange's epoch.
 cudaError_t launch_peer_allreduce(const PeerReduceLaunch& launch, bool pdl, cudaStream_t stream);
 
+// Two-shot all-reduce of a K-split GEMM output [M, N] whose partial tiles the GEMM has scattered
+// to the owners of their columns (launch_gemm_tc_pair with PairScatter).  Layout of such an
+// exchange buffer: the control block as above, `world` slots of [M, N / world] FP16 (slot r =
+// rank r's partial of the owner's columns), then the owner's reduced block [M, N / world].
+size_t peer_gemm_buffer_bytes(int64_t M, int64_t N, int world);
+// Two launches on `stream` (no programmatic dependent launch: they start when the stream's
+// earlier work, the scattering GEMM included, is complete): reduce the own columns, then gather
+// the peers' columns; y [M, N] ends up identical on all ranks.  Advances the exchange's epoch by 2.
+cudaError_t launch_peer_slice_allreduce(const PeerReduce& exchange, __half* y, int64_t M, int64_t N, int sm_count,
+                                        int* status, cudaStream_t stream);
+
 // ----- grouped decode GEMV (gemv_grouped.cu) ---------------------------------------------------
 struct GroupProblemDesc {
   const void* x;
@@ -139,7 +150,14 @@ cudaError_t launch_gemm_tc_small(const Problem& p, int* status_word, cudaStream_
 
 // ----- TMA + tcgen05 GEMM on pairs of CTAs, cta_group::2 (gemm_tc2.cu) ---------------------------
 bool gemm_tc_pair_supports(int64_t M, int64_t N, int64_t K);
-cudaError_t launch_gemm_tc_pair(const Problem& p, int* status_word, cudaStream_t stream, bool pdl, bool independent);
+// With `scatter` the output does not go to p.y: the tile of columns [o N / world, (o + 1) N / world)
+// is written to slot[o], row pitch N / world (this rank's slot in the exchange buffer of rank o).
+struct PairScatter {
+  __half* slot[8];
+  int world;
+};
+cudaError_t launch_gemm_tc_pair(const Problem& p, int* status_word, cudaStream_t stream, bool pdl, bool independent,
+                                const PairScatter* scatter = nullptr);
 
 // ----- tcgen05 GEMM with the weights passed through tensor memory (gemm_wt.cu) ------------------
 bool gemm_wt_supports(int64_t M, int64_t N, int64_t K);

@@ -128,7 +128,224 @@ __global__ void __launch_bounds__(kReduceThreads) peer_allreduce_kernel(const Re
   }
 }
 
+// ---------------------------------------------------------------------------------------------
+// Two-shot all-reduce of a K-split GEMM output [M, N] (large M).  Rank o owns the columns
+// [o N / world, (o + 1) N / world).  The GEMM's epilogue (gemm_tc2.cu) has already written every
+// rank's partial tile of those columns into rank o's exchange buffer, tile by tile while the GEMM
+// ran: slot r of the buffer = rank r's partial [M, owner_cols], FP16.  What is left:
+//   kernel 1 (reduce): tell every peer "my GEMM is complete" and wait for the same from them; add
+//     the `world` slots of the own columns in rank order (FP32 sums, one rounding to FP16); write
+//     the sums to y and to the `result` block of the own buffer; the last CTA tells every peer
+//     "my columns are reduced";
+//   kernel 2 (gather): wait for that message from every peer and copy their result blocks into y
+//     with vector loads over NVLink; the last CTA advances the epoch by two.
+// Every rank ends with the same bits in y.  A buffer serves one all-reduce at a time: the next
+// GEMM that scatters into it must be ordered after this rank's gather kernel (same stream, or an
+// event).  That suffices across ranks too: a peer raises its second flag only after it has read
+// its slots, and rewrites its result block only after every rank's next first flag, which a rank
+// raises after its own gather.
+struct SliceParams {
+  unsigned char* peers[kMaxPeers];
+  __half* y;
+  int rank, world;
+  int M, N, owner_cols;
+  int ctas_total;
+  int* status;
+};
+
+__device__ __forceinline__ uint4 load_relaxed_sys_u4(const void* ptr) {
+  uint4 v;
+  asm volatile("ld.relaxed.sys.global.v4.u32 {%0, %1, %2, %3}, [%4];"
+               : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w)
+               : "l"(ptr));
+  return v;
+}
+
+// Threads 0 .. world-1 (except `rank`) each wait, bounded, for flags[src] >= epoch in the own buffer.
+__device__ __forceinline__ void wait_for_peers(unsigned char* own, int rank, int world, unsigned int epoch,
+                                               int* status, int* timed_out) {
+  const int tid = threadIdx.x;
+  if (tid < world && tid != rank) {
+    const unsigned int* mine = reinterpret_cast<const unsigned int*>(own + kPeerFlagsOffset + tid * 128);
+    const long long start = clock64();
+    while (static_cast<int>(load_acquire_sys(mine) - epoch) < 0) {
+      if (clock64() - start > kWaitLimitCycles) {
+        atomicCAS(status, 0, kStatusPeerWait);
+        *timed_out = 1;
+        break;
+      }
+      __nanosleep(100);
+    }
+  }
+}
+
+__device__ __forceinline__ void accumulate_half8(float (&acc)[8], const uint4& v) {
+  const __half2* h = reinterpret_cast<const __half2*>(&v);
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    const float2 f = __half22float2(h[i]);
+    acc[2 * i] += f.x;
+    acc[2 * i + 1] += f.y;
+  }
+}
+
+__global__ void __launch_bounds__(kReduceThreads) peer_slice_reduce_kernel(const SliceParams p) {
+  __shared__ int timed_out;
+  const int tid = threadIdx.x;
+  unsigned char* own = p.peers[p.rank];
+  int* done = reinterpret_cast<int*>(own + kPeerDoneOffset);
+  const unsigned int epoch = *reinterpret_cast<volatile unsigned int*>(own + kPeerEpochOffset) + 1;
+  if (tid == 0) timed_out = 0;
+  __syncthreads();
+  // This kernel is launched without programmatic dependent launch: the GEMM before it in the
+  // stream is complete, its tiles are in the owners' buffers.
+  if (blockIdx.x == 0 && tid < p.world && tid != p.rank) {
+    __threadfence_system();
+    store_release_sys(reinterpret_cast<unsigned int*>(p.peers[tid] + kPeerFlagsOffset + p.rank * 128), epoch);
+  }
+  wait_for_peers(own, p.rank, p.world, epoch, p.status, &timed_out);
+  __syncthreads();
+
+  const size_t slice_bytes = static_cast<size_t>(p.M) * p.owner_cols * sizeof(__half);
+  const unsigned char* slots = own + kPeerBufferHeaderBytes;
+  unsigned char* result = own + kPeerBufferHeaderBytes + static_cast<size_t>(p.world) * slice_bytes;
+  const int chunks_per_row = p.owner_cols / 8;
+  const long long chunks = static_cast<long long>(p.M) * chunks_per_row;
+  const bool failed = timed_out != 0;
+  for (long long c = static_cast<long long>(blockIdx.x) * kReduceThreads + tid; c < chunks;
+       c += static_cast<long long>(gridDim.x) * kReduceThreads) {
+    uint4 out;
+    if (failed) {
+      out = make_uint4(0x7E007E00u, 0x7E007E00u, 0x7E007E00u, 0x7E007E00u);
+    } else {
+      uint4 part[kMaxPeers];
+#pragma unroll
+      for (int r = 0; r < kMaxPeers; ++r) {
+        if (r < p.world) part[r] = load_relaxed_sys_u4(slots + r * slice_bytes + c * 16);
+      }
+      float acc[8] = {0.0f, 0.0f, 0.0f, 0.0f, 0.0f, 0.0f, 0.0f, 0.0f};
+#pragma unroll
+      for (int r = 0; r < kMaxPeers; ++r) {
+        if (r < p.world) accumulate_half8(acc, part[r]);
+      }
+      __half2 h[4];
+#pragma unroll
+      for (int i = 0; i < 4; ++i) h[i] = __floats2half2_rn(acc[2 * i], acc[2 * i + 1]);
+      out = *reinterpret_cast<const uint4*>(h);
+    }
+    *reinterpret_cast<uint4*>(result + c * 16) = out;
+    const long long row = c / chunks_per_row;
+    const int col = static_cast<int>(c - row * chunks_per_row) * 8;
+    *reinterpret_cast<uint4*>(p.y + row * p.N + p.rank * p.owner_cols + col) = out;
+  }
+  __syncthreads();
+  if (tid == 0) {
+    __threadfence_system();
+    if (atomicAdd(done, 1) == p.ctas_total - 1) {
+      *done = 0;
+      __threadfence_system();
+      for (int r = 0; r < p.world; ++r) {
+        if (r != p.rank) {
+          store_release_sys(reinterpret_cast<unsigned int*>(p.peers[r] + kPeerFlagsOffset + p.rank * 128), epoch + 1);
+        }
+      }
+    }
+  }
+}
+
+__global__ void __launch_bounds__(kReduceThreads) peer_slice_gather_kernel(const SliceParams p) {
+  __shared__ int timed_out;
+  const int tid = threadIdx.x;
+  // Kernels that follow in the stream and use programmatic dependent launch may start now.
+  pdl_allow_next_kernel();
+  unsigned char* own = p.peers[p.rank];
+  int* done = reinterpret_cast<int*>(own + kPeerDoneOffset);
+  volatile unsigned int* epoch_word = reinterpret_cast<volatile unsigned int*>(own + kPeerEpochOffset);
+  const unsigned int epoch = *epoch_word + 2;
+  if (tid == 0) timed_out = 0;
+  __syncthreads();
+  wait_for_peers(own, p.rank, p.world, epoch, p.status, &timed_out);
+  __syncthreads();
+
+  const size_t slice_bytes = static_cast<size_t>(p.M) * p.owner_cols * sizeof(__half);
+  const size_t result_offset = kPeerBufferHeaderBytes + static_cast<size_t>(p.world) * slice_bytes;
+  const int chunks_per_row = p.owner_cols / 8;
+  const long long chunks = static_cast<long long>(p.M) * chunks_per_row;
+  const bool failed = timed_out != 0;
+  constexpr int kInFlight = 4;
+  const long long stride = static_cast<long long>(gridDim.x) * kReduceThreads;
+  for (int step = 1; step < p.world; ++step) {
+    const int r = (p.rank + step) % p.world;  // every rank starts at another peer
+    const unsigned char* src = p.peers[r] + result_offset;
+    for (long long c0 = static_cast<long long>(blockIdx.x) * kReduceThreads + tid; c0 < chunks; c0 += stride * kInFlight) {
+      uint4 v[kInFlight];
+#pragma unroll
+      for (int i = 0; i < kInFlight; ++i) {
+        const long long c = c0 + i * stride;
+        if (c < chunks) {
+          v[i] = failed ? make_uint4(0x7E007E00u, 0x7E007E00u, 0x7E007E00u, 0x7E007E00u)
+                        : load_relaxed_sys_u4(src + c * 16);
+        }
+      }
+#pragma unroll
+      for (int i = 0; i < kInFlight; ++i) {
+        const long long c = c0 + i * stride;
+        if (c < chunks) {
+          const long long row = c / chunks_per_row;
+          const int col = static_cast<int>(c - row * chunks_per_row) * 8;
+          *reinterpret_cast<uint4*>(p.y + row * p.N + r * p.owner_cols + col) = v[i];
+        }
+      }
+    }
+  }
+  __syncthreads();
+  if (tid == 0) {
+    __threadfence();
+    if (atomicAdd(done, 1) == p.ctas_total - 1) {
+      *done = 0;
+      *epoch_word = epoch;
+      __threadfence();
+    }
+  }
+}
+
 }  // namespace
+
+size_t peer_gemm_buffer_bytes(int64_t M, int64_t N, int world) {
+  if (M <= 0 || N <= 0 || world < 1) return 0;
+  // world slots of [M, N / world] plus the result block of the same size, FP16.
+  return kPeerBufferHeaderBytes + static_cast<size_t>(M) * N * sizeof(__half) +
+         static_cast<size_t>(M) * (N / world) * sizeof(__half);
+}
+
+cudaError_t launch_peer_slice_allreduce(const PeerReduce& ex, __half* y, int64_t M, int64_t N, int sm_count,
+                                        int* status, cudaStream_t stream) {
+  if (ex.world < 2 || ex.world > kMaxPeers || ex.rank < 0 || ex.rank >= ex.world || M < 1 || N % (8 * ex.world) != 0) {
+    return cudaErrorInvalidValue;
+  }
+  SliceParams kp;
+  for (int r = 0; r < kMaxPeers; ++r) {
+    kp.peers[r] = r < ex.world ? static_cast<unsigned char*>(ex.buffers[r]) : nullptr;
+  }
+  kp.y = y;
+  kp.rank = ex.rank;
+  kp.world = ex.world;
+  kp.M = static_cast<int>(M);
+  kp.N = static_cast<int>(N);
+  kp.owner_cols = static_cast<int>(N / ex.world);
+  kp.status = status;
+  const long long chunks = static_cast<long long>(M) * (kp.owner_cols / 8);
+  long long ctas = (chunks + kReduceThreads - 1) / kReduceThreads;
+  const long long cap = 4LL * (sm_count > 0 ? sm_count : 148);
+  if (ctas > cap) ctas = cap;
+  if (ctas < 1) ctas = 1;
+  kp.ctas_total = static_cast<int>(ctas);
+  peer_slice_reduce_kernel<<<static_cast<unsigned>(ctas), kReduceThreads, 0, stream>>>(kp);
+  cudaError_t err = cudaGetLastError();
+  if (err != cudaSuccess) return err;
+  peer_slice_gather_kernel<<<static_cast<unsigned>(ctas), kReduceThreads, 0, stream>>>(kp);
+  return cudaGetLastError();
+}
 
 cudaError_t launch_peer_allreduce(const PeerReduceLaunch& launch, bool pdl, cudaStream_t stream) {
   const PeerReduce& ex = launch.exchange;

@@ -29,7 +29,7 @@ from .linear import _validate_packed_weight
 
 class GraphedLinears:
     def __init__(self, layers, m=1, programmatic_dependent_launch=True, reduce=None, exchange=None,
-                 group=None, grouped=None):
+                 group=None, grouped=None, gemm_exchange=None):
         load_cuda_extension(required=True)
         layers = list(layers)
         if not layers:
@@ -88,6 +88,18 @@ class GraphedLinears:
             need = max(_ops._lib.lbl_w4a16_workspace_bytes(m, l.out_features, l.in_features, _ops.PATH_AUTO)
                        for l in layers)
             self.scratch = torch.zeros(max(need, 16), dtype=torch.uint8, device=device)
+        # Large M, K-split layers: with a ``PeerExchange.for_gemm`` the partial outputs leave the GEMM's
+        # epilogue for their owners over NVLink and the rest of the all-reduce (two small kernels)
+        # runs on a side stream beside the following GEMMs; without one NCCL sums the outputs.
+        self.gemm_exchange = gemm_exchange if (world > 1 and not grouped) else None
+        self.fused = [False] * len(layers)
+        if self.gemm_exchange is not None:
+            ex = self.gemm_exchange
+            for i, (layer, r) in enumerate(zip(layers, self.reduce)):
+                need = ex._lib.lbl_peer_gemm_buffer_bytes(m, layer.out_features, ex.world)
+                self.fused[i] = bool(r and m >= 256 and layer.in_features % 256 == 0
+                                     and layer.out_features % (256 * ex.world) == 0 and 0 < need <= ex.bytes)
+        self.side_stream = torch.cuda.Stream(device=device) if any(self.fused) else None
         self.stream = torch.cuda.Stream(device=device)
         self.graph = torch.cuda.CUDAGraph()
         previous = _ops._flags
@@ -115,12 +127,29 @@ class GraphedLinears:
             self.linear_group.run()
             return
         pending = []
-        for layer, x, y, reduce in zip(self.layers, self.xs, self.ys, self.reduce):
+        main = torch.cuda.current_stream(self.device)
+        exchanged = None  # event: the side stream has finished the previous fused all-reduce
+        for layer, x, y, reduce, fused in zip(self.layers, self.xs, self.ys, self.reduce, self.fused):
+            if fused:
+                # One all-reduce per exchange at a time: the scattering GEMM follows the previous finish.
+                if exchanged is not None:
+                    main.wait_event(exchanged)
+                _ops.gemm_scatter(x, layer.packed_weight, layer.scales, layer.zeros, self.gemm_exchange)
+                scattered = torch.cuda.Event()
+                scattered.record(main)
+                self.side_stream.wait_event(scattered)
+                with torch.cuda.stream(self.side_stream):
+                    _ops.gemm_allreduce_finish(y, self.gemm_exchange)
+                    exchanged = torch.cuda.Event()
+                    exchanged.record(self.side_stream)
+                continue
             _ops.linear_out(x, layer.packed_weight, layer.scales, layer.zeros, y, workspace=self.scratch)
             if reduce and self.world > 1:
                 import torch.distributed as dist
 
                 pending.append(dist.all_reduce(y, group=self.process_group, async_op=True))
+        if exchanged is not None:
+            main.wait_event(exchanged)
         for work in pending:
             work.wait()
 

@@ -60,7 +60,7 @@ class PeerExchange:
     """Exchange buffers of all ranks of ``group`` for the fused K-split all-reduce (same node,
     one process per GPU).  Creating one is a collective call.  ``max_n`` bounds ``out_features``."""
 
-    def __init__(self, max_n, device, group=None):
+    def __init__(self, max_n, device, group=None, gemm_shape=None):
         from . import _extension
 
         lib = _extension.native()
@@ -69,7 +69,14 @@ class PeerExchange:
         self.rank, self.world = _world(group)
         self.capacity_n = int(max_n)
         self.device = torch.device(device)
-        size = lib.lbl_peer_buffer_bytes(self.capacity_n)
+        if gemm_shape is None:
+            size = lib.lbl_peer_buffer_bytes(self.capacity_n)
+        else:
+            size = lib.lbl_peer_gemm_buffer_bytes(int(gemm_shape[0]), int(gemm_shape[1]), self.world)
+            if size == 0:
+                raise ValueError(f"no GEMM exchange for shape {tuple(gemm_shape)} on {self.world} ranks")
+        self.bytes = int(size)
+        self.gemm_shape = None if gemm_shape is None else (int(gemm_shape[0]), int(gemm_shape[1]))
         own = ctypes.c_void_p()
         self._check(lib.lbl_peer_buffer_create(size, self.device.index, ctypes.byref(own)))
         handle = (ctypes.c_ubyte * 64)()
@@ -90,6 +97,12 @@ class PeerExchange:
             pointers.append(mapped.value)
         self.pointers = (ctypes.c_void_p * self.world)(*pointers)
         dist.barrier(group=group)  # every rank has mapped every buffer before the first kernel
+
+    @classmethod
+    def for_gemm(cls, max_m, n, device, group=None):
+        """Exchange buffers for the large-M K-split GEMM with fused all-reduce: outputs of up to
+        ``max_m`` rows and ``n`` columns (``n`` a multiple of 256 times the number of ranks)."""
+        return cls(0, device, group, gemm_shape=(max_m, n))
 
     def _check(self, rc):
         if rc != 0:
@@ -146,17 +159,27 @@ class RowParallelLinear(torch.nn.Module):
     activation (or the full ``[M, K]`` with ``input_is_parallel=False``) and returns the
     all-reduced ``[M, N]``."""
 
-    def __init__(self, shard, group=None, input_is_parallel=True, exchange=None):
+    def __init__(self, shard, group=None, input_is_parallel=True, exchange=None, gemm_exchange=None):
         super().__init__()
         self.shard = shard
         self.group = group
         self.input_is_parallel = input_is_parallel
         self.exchange = exchange  # PeerExchange: fuse the all-reduce into the decode kernel
+        self.gemm_exchange = gemm_exchange  # PeerExchange.for_gemm: the same for large M
 
     @classmethod
-    def from_full(cls, layer, group=None, input_is_parallel=True, exchange=None):
+    def from_full(cls, layer, group=None, input_is_parallel=True, exchange=None, gemm_exchange=None):
         rank, world = _world(group)
-        return cls(shard_row_parallel(layer, rank, world), group, input_is_parallel, exchange)
+        return cls(shard_row_parallel(layer, rank, world), group, input_is_parallel, exchange, gemm_exchange)
+
+    def _fused_gemm(self, x):
+        ex, shard = self.gemm_exchange, self.shard
+        if ex is None or not x.is_cuda or x.dtype != torch.float16 or not x.is_contiguous():
+            return False
+        m, n = x.shape[0], shard.out_features
+        return (shard.group_size == 64 and m >= 256 and shard.in_features % 256 == 0
+                and n % (256 * ex.world) == 0
+                and 0 < ex._lib.lbl_peer_gemm_buffer_bytes(m, n, ex.world) <= ex.bytes)
 
     def _fused(self, x):
         shard = self.shard
@@ -185,6 +208,11 @@ class RowParallelLinear(torch.nn.Module):
 
             return _ops.gemv_allreduce(x, self.shard.packed_weight, self.shard.scales,
                                        self.shard.zeros, self.exchange)
+        if world > 1 and self._fused_gemm(x):
+            from . import _ops
+
+            return _ops.gemm_allreduce(x, self.shard.packed_weight, self.shard.scales, self.shard.zeros,
+                                       self.gemm_exchange)
         y = self.shard(x)
         if world > 1:
             dist.all_reduce(y, op=dist.ReduceOp.SUM, group=self.group)

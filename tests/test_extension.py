@@ -117,6 +117,40 @@ def test_group_argument_errors_need_no_gpu():
 
 
 @needs_library
+def test_gemm_allreduce_argument_errors_need_no_gpu():
+    lib = ctypes.CDLL(str(LIBRARY))
+    lib.lbl_last_error.restype = ctypes.c_char_p
+    p, i64, i32, sz = ctypes.c_void_p, ctypes.c_int64, ctypes.c_int, ctypes.c_size_t
+    lib.lbl_peer_gemm_buffer_bytes.restype = sz
+    lib.lbl_peer_gemm_buffer_bytes.argtypes = [i64, i64, i32]
+    lib.lbl_w4a16_gemm_scatter.argtypes = [p, p, p, p, i64, i64, i64, i32, i32, ctypes.POINTER(p), sz, ctypes.c_uint,
+                                           i32, p]
+    lib.lbl_peer_gemm_allreduce_finish.argtypes = [p, i64, i64, i32, i32, ctypes.POINTER(p), sz, i32, p]
+    # world slots of [M, N / world] FP16 + one result block + the 2 KiB control block
+    assert lib.lbl_peer_gemm_buffer_bytes(2048, 4096, 4) == 2048 + 2048 * 4096 * 2 + 2048 * 1024 * 2
+    assert lib.lbl_peer_gemm_buffer_bytes(2048, 4096, 3) == 0 and lib.lbl_peer_gemm_buffer_bytes(0, 4096, 2) == 0
+    size = lib.lbl_peer_gemm_buffer_bytes(512, 1024, 2)
+    buffers = (p * 2)(4096, 8192)
+    t = 1 << 20
+    assert lib.lbl_w4a16_gemm_scatter(t, t, t, t, 512, 1024, 512, 0, 1, buffers, size, 0, 0, None) == -1
+    assert b"rank/world" in lib.lbl_last_error()
+    assert lib.lbl_w4a16_gemm_scatter(t, t, t, t, 512, 768, 512, 0, 2, buffers, size, 0, 0, None) == -4
+    assert b"256 * world" in lib.lbl_last_error()
+    assert lib.lbl_w4a16_gemm_scatter(t, t, t, t, 512, 1024, 512, 0, 2, buffers, size - 16, 0, 0, None) == -3
+    assert b"exchange buffers hold" in lib.lbl_last_error()
+    assert lib.lbl_w4a16_gemm_scatter(t, t, t, t, 512, 1024, 320, 0, 2, buffers, size, 0, 0, None) == -4
+    assert b"K % 256" in lib.lbl_last_error()
+    assert lib.lbl_w4a16_gemm_scatter(t, t + 4, t, t, 512, 1024, 512, 0, 2, buffers, size, 0, 0, None) == -1
+    assert b"16-byte aligned" in lib.lbl_last_error()
+    buffers[1] = None
+    assert lib.lbl_peer_gemm_allreduce_finish(t, 512, 1024, 1, 2, buffers, size, 0, None) == -1
+    assert b"rank 1" in lib.lbl_last_error()
+    buffers[1] = 8192
+    assert lib.lbl_peer_gemm_allreduce_finish(t + 2, 512, 1024, 1, 2, buffers, size, 0, None) == -1
+    assert b"y is null or not 16-byte aligned" in lib.lbl_last_error()
+
+
+@needs_library
 def test_dispatcher_choices_and_scratch_sizes():
     from lowbitlinear_b200 import _ops
     from lowbitlinear_b200._extension import load_cuda_extension

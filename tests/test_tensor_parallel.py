@@ -184,3 +184,70 @@ def test_fused_allreduce_two_ranks(tmp_path):
         pytest.skip("needs two GPUs")
     mp.spawn(_fused_worker, args=(2, _free_port(), str(tmp_path)), nprocs=2, join=True)
     _check_fused(tmp_path, 2)
+
+
+def _fused_gemm_worker(rank, world, port, result_dir):
+    """K-split GEMM (large M) whose epilogue scatters the partial tiles to the owners of their
+    columns, followed by the two-kernel reduce + gather over peer memory."""
+    from lowbitlinear_b200 import _ops
+    from lowbitlinear_b200.graph import GraphedLinears
+    from lowbitlinear_b200.tensor_parallel import PeerExchange, shard_row_parallel
+
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), NCCL_NVLS_ENABLE="0")
+    torch.cuda.set_device(rank)
+    device = torch.device("cuda", rank)
+    dist.init_process_group("nccl", rank=rank, world_size=world)
+    try:
+        n, k = 1024, 512 * world
+        weight, _ = _layer(n, k, seed=11, std=0.05)
+        full = QuantizedLinear.from_float(weight)
+        exchange = PeerExchange.for_gemm(640, n, device)
+        on_gpu = QuantizedLinear.from_float(weight).to(device)
+        row = RowParallelLinear.from_full(on_gpu, gemm_exchange=exchange)
+        part = k // world
+        g = torch.Generator().manual_seed(5)
+        outputs, expected = [], []
+        for m in (640, 300, 512, 640):  # ragged last tile, a smaller call in between, reuse of the buffers
+            xi = torch.randn(m, k, generator=g).half()
+            outputs.append(row(xi[:, rank * part:(rank + 1) * part].contiguous().to(device)))
+            expected.append(full(xi).float())
+        # The same through the graph runner: the finish kernels run on a side stream.
+        shard = shard_row_parallel(on_gpu, rank, world)
+        runner = GraphedLinears([shard, shard], m=512, reduce=[True, True], gemm_exchange=exchange)
+        assert runner.fused == [True, True]
+        xa, xb = torch.randn(512, k, generator=g).half(), torch.randn(512, k, generator=g).half()
+        for _ in range(3):
+            runner.xs[0].copy_(xa[:, rank * part:(rank + 1) * part])
+            runner.xs[1].copy_(xb[:, rank * part:(rank + 1) * part])
+            runner.replay()
+        torch.cuda.synchronize()
+        outputs += [runner.ys[0].clone(), runner.ys[1].clone()]
+        expected += [full(xa).float(), full(xb).float()]
+        assert _ops.device_status(device) == 0, "a bounded wait expired"
+        dist.barrier()
+        exchange.close()
+        np.savez(Path(result_dir) / f"fused_gemm{rank}.npz",
+                 outputs=torch.cat(outputs).float().cpu().numpy(), expected=torch.cat(expected).numpy())
+    finally:
+        dist.destroy_process_group()
+
+
+def _check_fused_gemm(result_dir, world):
+    first = None
+    for rank in range(world):
+        r = np.load(Path(result_dir) / f"fused_gemm{rank}.npz")
+        # FP16 partial outputs (weights rounded to FP16, as the reference GEMM), FP32 sums over the
+        # ranks, one more FP16 rounding.
+        np.testing.assert_allclose(r["outputs"], r["expected"], atol=6e-3, rtol=2e-3)
+        if first is None:
+            first = r["outputs"]
+        assert np.array_equal(r["outputs"], first), "ranks must agree bit for bit"
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("world", [2, 4])
+def test_fused_gemm_allreduce(tmp_path, world):
+    if torch.cuda.device_count() < world:
+        pytest.skip(f"needs {world} GPUs")
+    mp.spawn(_fused_gemm_worker, args=(world, _free_port(), str(tmp_path)), nprocs=world, join=True)
+    _check_fused_gemm(tmp_path, world)
