@@ -772,13 +772,13 @@ def run_prefill(ctx, layers, reference):
     unit, per_layer = unit_and_amount("prefill", m, [0, 1, 2, 3])
     amount = per_layer * LAYERS
     value = amount / (ms_per_step * 1e-3)
-    ratio, source = traffic_ratio("w4a16_gemm_tc_kernel")
+    ratio, source = traffic_ratio("w4a16_gemm_tc_pair_kernel")
     algorithmic_per_launch = sum(linear_bytes(m, n, k) for _, n, k in SHAPES) / 4.0 / world
     roofline = {"bound": "tensor", "achieved": value / world, "peak": ctx.peaks["tflops_sustained"], "unit": "TFLOP/s",
                 "frac": value / world / ctx.peaks["tflops_sustained"],
                 "traffic": None if ratio is None else ratio * algorithmic_per_launch,
                 "traffic_unit": "DRAM bytes (read + write) per average launch", "traffic_source": source,
-                "kernel": "w4a16_gemm_tc_kernel", "peak_source": ctx.peaks["source"] + " (sustained bf16 GEMM)",
+                "kernel": "w4a16_gemm_tc_pair_kernel", "peak_source": ctx.peaks["source"] + " (sustained bf16 GEMM)",
                 "per_launch": "this GPU's flops of the step / 144 launches over the step's CUDA-event time / 144",
                 "fraction_of_nominal_2250": value / world / 2250.0}
     block = {"metric": metric_name("prefill"), "value": value, "unit": unit, "ms_per_step": ms_per_step,

@@ -62,6 +62,10 @@ constexpr int kTmemCols = 512;
 constexpr int kBarrierBytes = 256;
 constexpr int kSmemBytes = kStagesA * kStageBytesA + kStagesB * kStageBytesB + kBarrierBytes + 1024;
 constexpr int kStatusPairWait = 500;
+// The epilogue stages the CTA's FP16 tile (256 token rows x 256 columns) in the rings' memory;
+// 16 bytes of padding per row keep the lanes' 16-byte stores on different banks.
+constexpr int kOutPitch = kNPair * 2 + 16;
+static_assert(kTokensCta * kOutPitch <= kStagesA * kStageBytesA + kStagesB * kStageBytesB, "tile does not fit the rings");
 
 constexpr int kRelaySlots = 4;
 constexpr int kMaxScatterRanks = 8;
@@ -294,35 +298,54 @@ __global__ void __launch_bounds__(kThreads, 1)
     const int g = ((warp - 2) >> 2) & 1;        // token group (accumulator) handled by this warp
     const int column_part = (warp - 2) >> 3;    // with sixteen warps two share a quarter of an accumulator
     constexpr int kColumnParts = kDequantWarps / 8;
+    constexpr int kColsWarp = kNPair / kColumnParts;
     if (ok) {
-      const int m = m0 + g * 256 + quarter * 32 + lane;
-      __half* out_row;
-      if (p.owner_cols == 0) {
-        out_row = p.y + static_cast<size_t>(m < p.M ? m : 0) * p.N + n0;
-      } else {
-        const int owner = n0 / p.owner_cols;
-        out_row = p.scatter[owner] + static_cast<size_t>(m < p.M ? m : 0) * p.owner_cols + (n0 - owner * p.owner_cols);
-      }
+      // The accumulators are complete, so every stage of both rings has been read: the rings' shared
+      // memory now stages the FP16 tile, and rows leave it as whole 512-byte runs (a lane of the
+      // accumulator is a token row: written straight from registers, a warp's store would touch 32
+      // rows with 16 bytes each -- tolerable in local memory, very slow as NVLink packets).
+      const int row_cta = g * kTokensGroup + quarter * 32;  // first of this warp's 32 rows within the CTA's 256
+      uint8_t* stage = smem_a;
       const uint32_t taddr = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) + g * 256;
-      for (int c0 = column_part * (kNPair / kColumnParts); c0 < (column_part + 1) * (kNPair / kColumnParts); c0 += 32) {
+      const uint32_t my_row = smem_addr(stage + (row_cta + lane) * kOutPitch);
+      for (int c0 = column_part * kColsWarp; c0 < (column_part + 1) * kColsWarp; c0 += 32) {
         uint32_t v[32];
         tmem_load_32cols(taddr + c0, v);
         tmem_load_wait();
-        if (m < p.M) {
 #pragma unroll
-          for (int i = 0; i < 4; ++i) {
-            uint4 o;
-            __half2 h0 = __floats2half2_rn(__uint_as_float(v[8 * i + 0]), __uint_as_float(v[8 * i + 1]));
-            __half2 h1 = __floats2half2_rn(__uint_as_float(v[8 * i + 2]), __uint_as_float(v[8 * i + 3]));
-            __half2 h2 = __floats2half2_rn(__uint_as_float(v[8 * i + 4]), __uint_as_float(v[8 * i + 5]));
-            __half2 h3 = __floats2half2_rn(__uint_as_float(v[8 * i + 6]), __uint_as_float(v[8 * i + 7]));
-            o.x = *reinterpret_cast<uint32_t*>(&h0);
-            o.y = *reinterpret_cast<uint32_t*>(&h1);
-            o.z = *reinterpret_cast<uint32_t*>(&h2);
-            o.w = *reinterpret_cast<uint32_t*>(&h3);
-            *reinterpret_cast<uint4*>(out_row + c0 + 8 * i) = o;
-          }
+        for (int i = 0; i < 4; ++i) {
+          __half2 h0 = __floats2half2_rn(__uint_as_float(v[8 * i + 0]), __uint_as_float(v[8 * i + 1]));
+          __half2 h1 = __floats2half2_rn(__uint_as_float(v[8 * i + 2]), __uint_as_float(v[8 * i + 3]));
+          __half2 h2 = __floats2half2_rn(__uint_as_float(v[8 * i + 4]), __uint_as_float(v[8 * i + 5]));
+          __half2 h3 = __floats2half2_rn(__uint_as_float(v[8 * i + 6]), __uint_as_float(v[8 * i + 7]));
+          asm volatile("st.shared.v4.u32 [%0], {%1, %2, %3, %4};" ::"r"(my_row + (c0 + 8 * i) * 2),
+                       "r"(*reinterpret_cast<uint32_t*>(&h0)), "r"(*reinterpret_cast<uint32_t*>(&h1)),
+                       "r"(*reinterpret_cast<uint32_t*>(&h2)), "r"(*reinterpret_cast<uint32_t*>(&h3))
+                       : "memory");
         }
+      }
+      __syncwarp();
+      // Destination of the tile: y, or this rank's slot at the rank that owns the columns.
+      __half* out;
+      size_t pitch;
+      if (p.owner_cols == 0) {
+        out = p.y + n0;
+        pitch = static_cast<size_t>(p.N);
+      } else {
+        const int owner = n0 / p.owner_cols;
+        out = p.scatter[owner] + (n0 - owner * p.owner_cols);
+        pitch = static_cast<size_t>(p.owner_cols);
+      }
+      constexpr int kLanesPerRow = kColsWarp / 8;       // 16-byte pieces of a row's part
+      constexpr int kRowsPerStep = 32 / kLanesPerRow;
+      const int piece = lane % kLanesPerRow;
+      const int sub_row = lane / kLanesPerRow;
+      const int col = column_part * kColsWarp + piece * 8;
+#pragma unroll 4
+      for (int r = sub_row; r < 32; r += kRowsPerStep) {
+        const int m = m0 + g * 256 + quarter * 32 + r;
+        const uint4 piece_value = *reinterpret_cast<const uint4*>(stage + (row_cta + r) * kOutPitch + col * 2);
+        if (m < p.M) *reinterpret_cast<uint4*>(out + static_cast<size_t>(m) * pitch + col) = piece_value;
       }
       // Tiles sent to a peer: order them before whatever this GPU tells that peer afterwards.
       if (p.owner_cols != 0) __threadfence_system();
