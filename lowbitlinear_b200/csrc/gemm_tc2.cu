@@ -347,8 +347,9 @@ __global__ void __launch_bounds__(kThreads, 1)
         const uint4 piece_value = *reinterpret_cast<const uint4*>(stage + (row_cta + r) * kOutPitch + col * 2);
         if (m < p.M) *reinterpret_cast<uint4*>(out + static_cast<size_t>(m) * pitch + col) = piece_value;
       }
-      // Tiles sent to a peer: order them before whatever this GPU tells that peer afterwards.
-      if (p.owner_cols != 0) __threadfence_system();
+      // Tiles sent to a peer are ordered before whatever this GPU tells that peer afterwards by the
+      // end of the kernel: the exchange's first flag is raised by a later launch (a fence here would
+      // hold the SM until every store has been acknowledged across NVLink).
     }
   }
 
