@@ -230,11 +230,15 @@ __global__ void __launch_bounds__(kThreads, 1)
           mbar_wait_bounded(&bars->a_empty[s], (round - 1) & 1, abort_flag, p.status, kStatusPairWait + 1);
         }
         if (*abort_flag) break;
+#ifdef LBL_TC_SKIP_TMA  // ablation switch: the stage is handed on without its copies
+        mbar_arrive(&bars->a_full[s]);
+#else
         mbar_arrive_expect_tx(&bars->a_full[s], kStageBytesA);
         for (int g = 0; g < 2; ++g) {
           tma_load_2d(smem_a + s * kStageBytesA + g * (kStageBytesA / 2), &tmap_x, kb * kBK, m0 + g * 256,
                       &bars->a_full[s]);
         }
+#endif
       }
     }
   } else if (warp == 1) {
