@@ -1024,8 +1024,9 @@ def main():
     parser.add_argument("--impl", choices=("ours", "reference", "reference_gpu"), default="ours")
     parser.add_argument("--workload", choices=("stack", "decode", "prefill", "crossover", "prefill_sweep"),
                         default="stack")
-    parser.add_argument("--allreduce", choices=("fused", "nccl"), default="fused",
-                        help="prefill at N > 1: all-reduce of the Down output fused into the GEMM (peer memory) or NCCL")
+    parser.add_argument("--allreduce", choices=("fused", "nccl"), default="nccl",
+                        help="prefill at N > 1: asynchronous NCCL all-reduces of the Down output (the faster of the "
+                             "two on two GPUs, equal on four) or the all-reduce fused into the GEMM over peer memory")
     parser.add_argument("--emit", default=None, help=argparse.SUPPRESS)
     args = parser.parse_args()
     if args.impl == "reference":
