@@ -738,31 +738,52 @@ def run_prefill(ctx, layers, reference):
     host_x = torch.empty(x_elems, dtype=torch.float16).pin_memory()
     host_x.copy_(torch.cat([runner.xs[i].reshape(-1) for i in range(chunk)]).cpu())
     host_y = torch.empty(y_elems, dtype=torch.float16).pin_memory()
-    dev_x = torch.empty(x_elems, dtype=torch.float16, device=device)
-    dev_y = torch.empty(y_elems, dtype=torch.float16, device=device)
-    x_views, y_views, xo, yo = [], [], 0, 0
-    for i in range(chunk):
-        x_views.append(dev_x[xo:xo + runner.xs[i].numel()].view_as(runner.xs[i]))
-        y_views.append(dev_y[yo:yo + runner.ys[i].numel()].view_as(runner.ys[i]))
-        xo += runner.xs[i].numel()
-        yo += runner.ys[i].numel()
+    # Two sets of device buffers and three streams: while layer c computes, the activations of layer
+    # c + 1 come up and the outputs of layer c - 1 go down.  Every layer still makes its own copies.
+    up, compute, down = (torch.cuda.Stream(device=device) for _ in range(3))
+    sets = []
+    for _ in range(2):
+        dev_x = torch.empty(x_elems, dtype=torch.float16, device=device)
+        dev_y = torch.empty(y_elems, dtype=torch.float16, device=device)
+        x_views, y_views, xo, yo = [], [], 0, 0
+        for i in range(chunk):
+            x_views.append(dev_x[xo:xo + runner.xs[i].numel()].view_as(runner.xs[i]))
+            y_views.append(dev_y[yo:yo + runner.ys[i].numel()].view_as(runner.ys[i]))
+            xo += runner.xs[i].numel()
+            yo += runner.ys[i].numel()
+        sets.append({"x": dev_x, "y": dev_y, "xv": x_views, "yv": y_views, "uploaded": torch.cuda.Event(),
+                     "computed": torch.cuda.Event(), "downloaded": torch.cuda.Event()})
     scratch = runner.scratch
 
     def e2e_step():
         for c in range(LAYERS):
-            dev_x.copy_(host_x, non_blocking=True)
-            for j in range(chunk):
-                name, layer = layers[c * chunk + j]
-                if fused and name == "down":
-                    _ops.gemm_allreduce(x_views[j], layer.packed_weight, layer.scales, layer.zeros, gemm_exchange,
-                                        out=y_views[j])
-                    continue
-                _ops.linear_out(x_views[j], layer.packed_weight, layer.scales, layer.zeros, y_views[j],
-                                workspace=scratch)
-                if world > 1 and name == "down":
-                    ctx.dist.all_reduce(y_views[j])
-            host_y.copy_(dev_y, non_blocking=True)
-        torch.cuda.current_stream().synchronize()
+            b = sets[c & 1]
+            with torch.cuda.stream(up):
+                if c >= 2:
+                    up.wait_event(b["computed"])  # layer c - 2 has read this buffer
+                b["x"].copy_(host_x, non_blocking=True)
+                b["uploaded"].record(up)
+            with torch.cuda.stream(compute):
+                compute.wait_event(b["uploaded"])
+                if c >= 2:
+                    compute.wait_event(b["downloaded"])  # the outputs of layer c - 2 have left
+                for j in range(chunk):
+                    name, layer = layers[c * chunk + j]
+                    if fused and name == "down":
+                        _ops.gemm_allreduce(b["xv"][j], layer.packed_weight, layer.scales, layer.zeros, gemm_exchange,
+                                            out=b["yv"][j])
+                        continue
+                    _ops.linear_out(b["xv"][j], layer.packed_weight, layer.scales, layer.zeros, b["yv"][j],
+                                    workspace=scratch)
+                    if world > 1 and name == "down":
+                        ctx.dist.all_reduce(b["yv"][j])
+                b["computed"].record(compute)
+            with torch.cuda.stream(down):
+                down.wait_event(b["computed"])
+                host_y.copy_(b["y"], non_blocking=True)
+                b["downloaded"].record(down)
+        down.synchronize()
+        compute.synchronize()
 
     e2e_ms = ctx.wall_steps(e2e_step, max(2, min(args.steps, 5)))
     status = _ops.device_status(device)
@@ -785,8 +806,9 @@ def run_prefill(ctx, layers, reference):
              "stats": summary(per_step), "roofline": roofline, "clocks": clocks,
              "e2e": {"value": amount / (e2e_ms * 1e-3), "unit": unit, "ms_per_step": e2e_ms,
                      "h2d_bytes_per_step": int(x_elems * 2 * LAYERS), "d2h_bytes_per_step": int(y_elems * 2 * LAYERS),
-                     "api": "lowbitlinear_b200._ops.linear_out per linear, eager, one layer's pinned host activations "
-                            "in and host outputs out at a time"},
+                     "api": "lowbitlinear_b200._ops.linear_out per linear, eager; per layer its pinned host activations "
+                            "in and its host outputs out, on upload / compute / download streams with two sets of "
+                            "device buffers (the copies of neighbouring layers overlap the GEMMs)"},
              "gpu_launches": (len(layers) + (2 * LAYERS if fused else 0)) * args.steps,
              "launch": "CUDA graph of 144 launches" + (
                  "" if world == 1 else
