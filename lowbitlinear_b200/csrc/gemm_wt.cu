@@ -142,14 +142,6 @@ __device__ __forceinline__ void tmem_store_wait() {
   asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
 }
 
-__device__ __forceinline__ void tma_load_3d_plain(void* smem_dst, const CUtensorMap* map, int c0, int c1,
-                                                  int c2, uint64_t* bar) {
-  asm volatile(
-      "cp.async.bulk.tensor.3d.shared::cluster.global.tile.mbarrier::complete_tx::bytes "
-      "[%0], [%1, {%2, %3, %4}], [%5];" ::"r"(smem_addr(smem_dst)),
-      "l"(map), "r"(c0), "r"(c1), "r"(c2), "r"(smem_addr(bar))
-      : "memory");
-}
 
 __global__ void __launch_bounds__(kThreads, 1)
     w4a16_gemm_wt_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_constant__ CUtensorMap tmap_w,
@@ -246,7 +238,7 @@ __global__ void __launch_bounds__(kThreads, 1)
 #else
         mbar_arrive_expect_tx(&bars->full[s], static_cast<uint32_t>(x_stage_bytes + kPackedTileBytes));
         tma_load_2d(smem_x + s * x_stage_bytes, &tmap_x, (kb_begin + kb) * kBK, m0, &bars->full[s]);
-        tma_load_3d_plain(smem_w + s * kPackedTileBytes, &tmap_w, 0, kb_begin + kb, n0, &bars->full[s]);
+        tma_load_3d(smem_w + s * kPackedTileBytes, &tmap_w, 0, kb_begin + kb, n0, &bars->full[s]);
 #endif
       }
     }

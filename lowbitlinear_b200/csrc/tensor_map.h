@@ -25,6 +25,15 @@ __device__ __forceinline__ void tma_load_2d(void* smem_dst, const CUtensorMap* m
       : "memory");
 }
 
+__device__ __forceinline__ void tma_load_3d(void* smem_dst, const CUtensorMap* map, int c0, int c1, int c2,
+                                            uint64_t* bar) {
+  asm volatile(
+      "cp.async.bulk.tensor.3d.shared::cluster.global.tile.mbarrier::complete_tx::bytes "
+      "[%0], [%1, {%2, %3, %4}], [%5];" ::"r"(static_cast<uint32_t>(__cvta_generic_to_shared(smem_dst))),
+      "l"(map), "r"(c0), "r"(c1), "r"(c2), "r"(static_cast<uint32_t>(__cvta_generic_to_shared(bar)))
+      : "memory");
+}
+
 // Three-dimensional tiled load with an L2 eviction policy (see l2_evict_first_policy): weights are read once
 // per call, so they should be the first lines the L2 gives up, not the activations and results
 // that the neighbouring kernels are about to touch.
