@@ -629,6 +629,17 @@ def run_decode(ctx, layers, reference):
                       "eager_forward_ms_per_step": eager_ms}
         del plain
 
+    # ---- secondary at N > 1: the same step without the all-reduce kernel (not a valid result, the
+    # Down outputs stay partial): what the collective adds to the step.
+    without_collective = None
+    if world > 1:
+        bare = GraphedLinears(modules, m=1)
+        bare.x_flat.copy_(runner.x_flat)
+        bare_total, _, _ = ctx.timed_replays(bare.replay, args.steps, 3)
+        without_collective = {"ms_per_step": bare_total / args.steps,
+                              "what": "the grouped launch alone, no all-reduce kernel (partial Down outputs)"}
+        del bare
+
     status = _ops.device_status(device)
     if status != 0:
         raise SystemExit(f"device status {status}: a bounded wait expired inside a kernel")
@@ -661,7 +672,7 @@ def run_decode(ctx, layers, reference):
              "gpu_launches": launches * args.steps,
              "launch": ("one grouped launch (lbl_w4a16_group_run) over the 144 independent linears"
                         + ("" if world == 1 else " + one all-reduce kernel over NVLink peer memory for the 36 Down outputs")),
-             "per_linear_launch": per_linear,
+             "per_linear_launch": per_linear, "without_collective": without_collective,
              "parity": {"rel_l2_vs_cpu_reference": parity, "tolerance": TOLERANCE, "checker": info["kind"]}}
     return block, runner, exchange
 
@@ -728,6 +739,19 @@ def run_prefill(ctx, layers, reference):
     note("prefill: timed region")
     total_ms, per_step, clocks = ctx.timed_replays(runner.replay, args.steps, args.warmup)
     ms_per_step = total_ms / args.steps
+    without_collective = None
+    if world > 1:
+        # Secondary: the same 144 launches without the all-reduces (partial Down outputs, not a
+        # valid result): what the collective adds to the step.
+        saved = runner.x_flat.clone()
+        del runner
+        bare = GraphedLinears(modules, m=m)
+        bare.x_flat.copy_(saved)
+        bare_total, _, _ = ctx.timed_replays(bare.replay, args.steps, 3)
+        without_collective = {"ms_per_step": bare_total / args.steps,
+                              "what": "the 144 GEMM launches alone, no all-reduce (partial Down outputs)"}
+        runner = bare  # the end-to-end leg below only needs its buffers' shapes and scratch
+        del saved
 
     # ---- end to end: one layer at a time through the same pinned buffers (the activations of a
     # whole step would need 9 GB of pinned memory), so every layer is fed layer 0's activation
@@ -815,6 +839,7 @@ def run_prefill(ctx, layers, reference):
                  " (Down: GEMM whose epilogue scatters its partial tiles to the owner ranks over NVLink) + 2 x 36 "
                  "reduce / gather kernels over peer memory on a side stream" if fused else
                  " with 36 NCCL all-reduces, issued asynchronously"),
+             "without_collective": without_collective,
              "parity": {"rel_l2_vs_cpu_reference": parity, "tolerance": TOLERANCE}}
     if gemm_exchange is not None:
         del runner
@@ -853,7 +878,8 @@ def run_stack(args):
             "higher_is_better": True, "scaling": "strong", "vs_baseline": None,
             "dtype": "f16 activations x int4 weights, f32 accumulate", "data": "synthetic",
             "config": config_of(args.workload, ctx.world)}
-    for key in ("stats", "roofline", "clocks", "e2e", "gpu_launches", "launch", "per_linear_launch", "parity"):
+    for key in ("stats", "roofline", "clocks", "e2e", "gpu_launches", "launch", "per_linear_launch",
+                "without_collective", "parity"):
         if key in head:
             line[key] = head[key]
     line["cpu_baseline"] = cpu_baseline if ctx.world == 1 else None
