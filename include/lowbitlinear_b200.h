@@ -154,6 +154,12 @@ int lbl_w4a16_gemv_noalloc(const void* x, const int32_t* packed_w, const float* 
 size_t lbl_peer_buffer_bytes(int64_t max_n);
 int lbl_peer_buffer_create(size_t bytes, int device, void** buffer);
 int lbl_peer_buffer_export(const void* buffer, void* handle64);
+/* Diagnostics: copies `bytes` at `offset` of the buffer's 2 KiB control block to the host
+ * (synchronous).  Bytes 1536..2047 hold eight records of eight 64-bit %globaltimer stamps when the
+ * library was built with -D LBL_TRACE_EXCHANGE (start and end of the grouped GEMV; entry, end of
+ * the wait for the GEMV, flags complete, sums complete and epoch update of the all-reduce kernel);
+ * zeros otherwise. */
+int lbl_peer_buffer_peek(const void* buffer, size_t offset, void* host_dst, size_t bytes, int device);
 int lbl_peer_buffer_open(const void* handle64, int device, void** buffer);
 int lbl_peer_buffer_close(void* buffer, int device);
 int lbl_peer_buffer_destroy(void* buffer, int device);

@@ -84,6 +84,8 @@ def bind(path):
     lib.lbl_peer_buffer_create.argtypes = [sz, i32, ctypes.POINTER(p)]
     lib.lbl_peer_buffer_export.restype = i32
     lib.lbl_peer_buffer_export.argtypes = [p, p]
+    lib.lbl_peer_buffer_peek.restype = i32
+    lib.lbl_peer_buffer_peek.argtypes = [p, sz, p, sz, i32]
     lib.lbl_peer_buffer_open.restype = i32
     lib.lbl_peer_buffer_open.argtypes = [p, i32, ctypes.POINTER(p)]
     lib.lbl_peer_buffer_close.restype = i32

@@ -559,6 +559,17 @@ int lbl_peer_buffer_create(size_t bytes, int device, void** buffer) {
   return LBL_OK;
 }
 
+int lbl_peer_buffer_peek(const void* buffer, size_t offset, void* host_dst, size_t bytes, int device) {
+  if (buffer == nullptr || host_dst == nullptr || offset + bytes > lbl::kPeerBufferHeaderBytes) {
+    return fail(LBL_ERR_INVALID, "peek reads the %zu-byte control block only", lbl::kPeerBufferHeaderBytes);
+  }
+  DeviceScope scope(device);
+  if (!scope.ok()) return fail(LBL_ERR_CUDA, "cannot make device %d current", device);
+  const cudaError_t err = cudaMemcpy(host_dst, static_cast<const unsigned char*>(buffer) + offset, bytes, cudaMemcpyDeviceToHost);
+  if (err != cudaSuccess) return fail_cuda(err, "cudaMemcpy(control block)");
+  return LBL_OK;
+}
+
 int lbl_peer_buffer_export(const void* buffer, void* handle64) {
   static_assert(sizeof(cudaIpcMemHandle_t) == 64, "IPC handle size");
   if (buffer == nullptr || handle64 == nullptr) return fail(LBL_ERR_INVALID, "null argument");

@@ -142,4 +142,11 @@ __device__ __forceinline__ void nibbles_as_subnormal_half2(uint32_t word, uint32
 }
 constexpr float kNibbleUnit = 16777216.0f;  // 2^24: the MMA sees q * 2^-24
 
+// Nanoseconds of the GPU's global timer (measurement builds only).
+__device__ __forceinline__ unsigned long long global_timer_ns() {
+  unsigned long long t;
+  asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+  return t;
+}
+
 }  // namespace lbl

@@ -98,6 +98,14 @@ __global__ void __launch_bounds__(kThreads, 2) w4a16_gemv_grouped_kernel(const G
   }
   __syncthreads();
   pdl_allow_next_kernel();
+#ifdef LBL_TRACE_EXCHANGE  // measurement build: time stamps in the exchange buffer's control block
+  unsigned long long* trace = nullptr;
+  if (p.epoch_word != nullptr) {
+    const unsigned int e = *reinterpret_cast<const volatile unsigned int*>(p.epoch_word);
+    trace = reinterpret_cast<unsigned long long*>(reinterpret_cast<unsigned char*>(const_cast<unsigned int*>(p.epoch_word)) - 4 + 1536) + (e % 8) * 8;
+    if (blockIdx.x == 0 && threadIdx.x == 0) trace[0] = global_timer_ns();
+  }
+#endif
 
   const int seg_begin = __ldg(&p.first_segment[blockIdx.x]);
   const int seg_end = __ldg(&p.first_segment[blockIdx.x + 1]);
@@ -177,6 +185,9 @@ __global__ void __launch_bounds__(kThreads, 2) w4a16_gemv_grouped_kernel(const G
         }
       }
     }
+#ifdef LBL_TRACE_EXCHANGE
+    if (trace != nullptr && lane == 0) atomicMax(trace + 1, global_timer_ns());
+#endif
     return;
   }
 

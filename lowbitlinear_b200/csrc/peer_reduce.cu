@@ -57,12 +57,20 @@ __global__ void __launch_bounds__(kReduceThreads) peer_allreduce_kernel(const Re
   __shared__ int timed_out;
   const int tid = threadIdx.x;
   pdl_allow_next_kernel();
+#ifdef LBL_TRACE_EXCHANGE
+  const unsigned long long entered = global_timer_ns();
+#endif
   // This GPU's partial sums come from the previous kernel in the stream.
   pdl_wait_for_previous_kernel();
   unsigned char* own = p.peers[p.rank];
   int* done = reinterpret_cast<int*>(own + kPeerDoneOffset);
   volatile unsigned int* epoch_word = reinterpret_cast<volatile unsigned int*>(own + kPeerEpochOffset);
   const unsigned int epoch = *epoch_word + 1;
+#ifdef LBL_TRACE_EXCHANGE  // measurement build: time stamps in the control block, see gemv_grouped.cu
+  unsigned long long* trace = reinterpret_cast<unsigned long long*>(own + 1536) + ((epoch - 1) % 8) * 8;
+  const bool first_block = blockIdx.x == 0 && blockIdx.y == 0 && tid == 0;
+  if (first_block) trace[2] = entered, trace[3] = global_timer_ns();
+#endif
   if (tid == 0) timed_out = 0;
   __syncthreads();
   if (tid < p.world && tid != p.rank) {
@@ -82,6 +90,9 @@ __global__ void __launch_bounds__(kReduceThreads) peer_allreduce_kernel(const Re
     }
   }
   __syncthreads();
+#ifdef LBL_TRACE_EXCHANGE
+  if (first_block) trace[4] = global_timer_ns();
+#endif
 
   const ReduceSegment seg = p.segments[blockIdx.y];
   const size_t vec = static_cast<size_t>(epoch & 1) * p.capacity_n + seg.offset;
@@ -119,11 +130,17 @@ __global__ void __launch_bounds__(kReduceThreads) peer_allreduce_kernel(const Re
   // The last CTA to finish opens the next epoch.
   __syncthreads();
   if (tid == 0) {
+#ifdef LBL_TRACE_EXCHANGE
+    atomicMax(trace + 5, global_timer_ns());
+#endif
     __threadfence();
     if (atomicAdd(done, 1) == p.ctas_total - 1) {
       *done = 0;
       *epoch_word = epoch;
       __threadfence();
+#ifdef LBL_TRACE_EXCHANGE
+      trace[6] = global_timer_ns();
+#endif
     }
   }
 }

@@ -5,6 +5,7 @@
     python -m lowbitlinear_b200.profile --operator gemm  --shape 16x4096x4096 --path gemm_tc_small
     python -m lowbitlinear_b200.profile --operator group --layers 2 --launches 3
     python -m lowbitlinear_b200.profile --operator quantize --shape 1x8192x4096 --launches 3
+    torchrun --nproc-per-node 2 -m lowbitlinear_b200.profile --operator exchange_trace --layers 36
 
 Plays the role of the reference's ``benchmarks/profile_w4a16.py``: inputs are prepared and the
 result is checked against an FP32 evaluation first, then the kernel is launched ``--launches``
@@ -13,7 +14,12 @@ HBM rather than the L2).  ``--path`` forces one kernel of the dispatcher (generi
 gemv_splitk, gemm_tc, gemm_tc_small); ``--operator group`` runs the grouped decode launch over
 ``--layers`` Qwen3-8B-shaped layers (four linears each, 120 MB of weights per layer);
 ``--operator quantize`` runs the device quantiser on an FP16 weight of the given N x K.
-It reports no latency: timing under a profiler means nothing.  Keep the case small (one kernel,
+``--operator exchange_trace`` (one process per GPU under torchrun; library built with
+``python -m lowbitlinear_b200.build --force -D LBL_TRACE_EXCHANGE``) replays the tensor-parallel
+decode step of ``--layers`` layers and prints, per replay, the %globaltimer stamps that the grouped
+GEMV and the all-reduce kernel leave in the exchange buffer's control block -- a timeline of the
+step, not run under a profiler.
+The other operators report no latency: timing under a profiler means nothing.  Keep the case small (one kernel,
 a few launches, a few hundred MB) when capturing with
 ``ncu --set full --clock-control none -k regex:<kernel> -s <skip> -c <count>``.
 """
@@ -40,9 +46,69 @@ def rel_l2(actual, expected):
     return ((actual.float() - expected.float()).norm() / expected.float().norm()).item()
 
 
+def exchange_trace(args):
+    """Timeline of the tensor-parallel decode step from the stamps of a trace build."""
+    import ctypes
+    import os
+
+    import torch.distributed as dist
+
+    from .graph import GraphedLinears
+    from .tensor_parallel import PeerExchange
+
+    rank, world = int(os.environ["RANK"]), int(os.environ["WORLD_SIZE"])
+    local = int(os.environ.get("LOCAL_RANK", rank))
+    torch.cuda.set_device(local)
+    device = torch.device("cuda", local)
+    dist.init_process_group("nccl")
+    g = torch.Generator(device=device).manual_seed(args.seed + rank)
+    layers, reduce = [], []
+    for _ in range(args.layers):
+        for i, (n, k) in enumerate(LAYER_SHAPES):
+            rows, cols = (n, k // world) if i == 3 else (n // world, k)  # Down is cut along K, the others along N
+            layers.append(QuantizedLinear.from_float((torch.randn(rows, cols, device=device, generator=g) * 0.02).half()))
+            reduce.append(i == 3)
+    exchange = PeerExchange(max_n=args.layers * LAYER_SHAPES[3][0], device=device)
+    runner = GraphedLinears(layers, m=1, reduce=reduce, exchange=exchange)
+    runner.x_flat.copy_(torch.randn(runner.x_flat.numel(), device=device, generator=g).half())
+    for _ in range(10):
+        runner.replay()
+    torch.cuda.synchronize()
+    dist.barrier()
+    torch.cuda.synchronize()
+    for _ in range(max(8, args.launches)):
+        runner.replay()
+    torch.cuda.synchronize()
+    stamps = (ctypes.c_ulonglong * 64)()
+    rc = _ops._lib.lbl_peer_buffer_peek(exchange.pointers[rank], 1536, stamps, 512, local)
+    records = sorted(([stamps[i * 8 + j] for j in range(8)] for i in range(8)), key=lambda q: q[0])
+    names = ("gemv_end", "allreduce_entered", "gemv_complete_seen", "flags_complete", "sums_complete", "epoch_updated")
+    lines = []
+    for i, q in enumerate(records):
+        if q[0] == 0:
+            continue
+        parts = [f"{name} {(q[j + 1] - q[0]) / 1e3:.1f}" for j, name in enumerate(names)]
+        if i + 1 < len(records):
+            parts.append(f"next_step_starts {(records[i + 1][0] - q[0]) / 1e3:.1f}")
+        lines.append("  ".join(parts))
+    gathered = [None] * world
+    dist.all_gather_object(gathered, (rc, lines))
+    if rank == 0:
+        print(f"decode step of {args.layers} layers on {world} GPUs; microseconds after the start of the grouped GEMV")
+        for r, (code, rows) in enumerate(gathered):
+            if code != 0 or not rows:
+                print(f"rank {r}: no stamps (library not built with -D LBL_TRACE_EXCHANGE?)")
+            for row in rows:
+                print(f"rank {r}: {row}")
+    torch.cuda.synchronize()
+    dist.barrier()
+    exchange.close()
+    dist.destroy_process_group()
+
+
 def main(argv=None):
     parser = argparse.ArgumentParser(description=__doc__, formatter_class=argparse.RawDescriptionHelpFormatter)
-    parser.add_argument("--operator", choices=("gemv", "gemm", "group", "quantize"), required=True)
+    parser.add_argument("--operator", choices=("gemv", "gemm", "group", "quantize", "exchange_trace"), required=True)
     parser.add_argument("--shape", default=None, help="MxNxK")
     parser.add_argument("--path", choices=tuple(v for v in _ops.PATH_NAMES.values() if v != "auto"), default=None)
     parser.add_argument("--layers", type=int, default=2)
@@ -54,6 +120,8 @@ def main(argv=None):
         raise SystemExit("no CUDA GPU")
     load_cuda_extension(required=True)
     torch.backends.cuda.matmul.allow_tf32 = False
+    if args.operator == "exchange_trace":
+        return exchange_trace(args)
     device = torch.device("cuda", 0)
     g = torch.Generator(device=device).manual_seed(args.seed)
 
