@@ -114,13 +114,18 @@ int select_path(int64_t M, int64_t N, int64_t K, int op, int sm_count) {
   // Measured (B200): with 9..128 rows of activations the small-M tensor-core GEMM wins wherever
   // the 256-wide tiles of the large one cannot fill the SMs (N < 16384), and up to M = 32 beyond.
   const bool wide = N >= 16384;
-  if (M >= kTcSmallMinM && lbl::gemm_tc_small_supports(M, N, K) && (!wide || M <= 32 || !tc_ok)) {
+  // On a wide shape the streaming kernel still wins at 9..16 rows when the whole activation operand
+  // fits its shared memory (Gate/Up, M = 16: 40 us against 55 and 62 for the tensor-core GEMMs).
+  const bool stream_wide = wide && M <= 16 && skinny_ok && M * K * 2 <= lbl::kSkinnyOperandBytes;
+  if (M >= kTcSmallMinM && lbl::gemm_tc_small_supports(M, N, K) && (!wide || M <= 32 || !tc_ok) && !stream_wide) {
     return LBL_PATH_GEMM_TC_SMALL;
   }
   // A long K whose activations do not fit the streaming kernel's operand budget is split along K
   // there (ordered fix-up); from six rows on the small tensor-core GEMM is faster (Down, M = 8:
-  // 29 against 36 us).
-  if (M >= 6 && M * K * 2 > 65536 && !wide && lbl::gemm_tc_small_supports(M, N, K)) return LBL_PATH_GEMM_TC_SMALL;
+  // 29 against 34 us).
+  if (M >= 6 && M * K * 2 > lbl::kSkinnyOperandBytes && !wide && lbl::gemm_tc_small_supports(M, N, K)) {
+    return LBL_PATH_GEMM_TC_SMALL;
+  }
   // More than 128 rows of activations on a shape whose 256 x 256 tiles would leave most SMs idle
   // (less than half a wave: small N, a tensor-parallel shard): the tensor-memory GEMM cuts K into
   // slices until the SMs are busy.  Also the only tensor-core kernel for N % 256 == 128.
@@ -141,7 +146,7 @@ int select_path(int64_t M, int64_t N, int64_t K, int op, int sm_count) {
     const int64_t waves_tc = (tc_ctas + sm_count - 1) / sm_count;
     if (10 * waves_pair <= 12 * waves_tc) return LBL_PATH_GEMM_TC_PAIR;
   }
-  if (tc_ok && (M >= kTcMinM || (wide && M >= 9) || !skinny_ok)) return LBL_PATH_GEMM_TC;
+  if (tc_ok && (M >= kTcMinM || (wide && M >= 9 && !stream_wide) || !skinny_ok)) return LBL_PATH_GEMM_TC;
   if (skinny_ok) {
     lbl::SkinnyPlan plan;
     if (lbl::skinny_make_plan(M, N, K, -1, sm_count, &plan)) {

@@ -51,6 +51,9 @@ struct SkinnyPlan {
 };
 
 constexpr int kSkinnyMaxM = 32;
+// Largest activation operand (M * kseg * 2 bytes) the streaming kernel keeps in shared memory; a
+// longer K is cut into segments that meet in scratch memory.
+constexpr int kSkinnyOperandBytes = 128 * 1024;
 // Split-K scratch layout: a fixed region of arrival counters (one int per 16-row tile) at the
 // start, partial sums behind it.  The counter region never moves, whatever the problem, so a
 // buffer that was zeroed once stays valid for every later call: counters are left at zero by

@@ -44,7 +44,10 @@ constexpr int kThreads = kConsumerThreads + 32;
 constexpr int kMaxSlots = 8;
 constexpr int kHeaderBytes = 384;
 constexpr int kMaxStageK = 2048;
-constexpr int kXfBudgetBytes = 64 * 1024;   // activation operand kept in shared memory
+// Activation operand kept in shared memory.  Up to 64 KB two CTAs share an SM; a larger operand
+// leaves room for one, which still beats cutting K (Down at M = 4: 18 against 24 us; Gate/Up at
+// M = 16: 40 against 82 us).
+constexpr int kXfBudgetBytes = kSkinnyOperandBytes;
 constexpr int kSmemBudgetTwoCtas = 110 * 1024;
 constexpr int kSmemBudgetOneCta = 200 * 1024;
 

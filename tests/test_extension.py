@@ -165,13 +165,16 @@ def test_dispatcher_choices_and_scratch_sizes():
         assert name(1, 4096, 4096) == "gemv"
         assert name(1, 4096, 12288) == "gemv"
         assert name(1, 512, 4096) == "gemv_splitk"     # a tensor-parallel shard: 32 row tiles
-        assert name(4, 4096, 12288) == "gemv_splitk"   # activations of one segment must fit on chip
-        assert name(8, 4096, 12288) == "gemm_tc_small" # ... and from six rows on the tensor cores are faster
+        assert name(4, 4096, 12288) == "gemv"          # 96 KB of activations still fit one CTA per SM
+        assert name(8, 4096, 12288) == "gemm_tc_small" # 192 KB do not: K would be cut, the tensor cores are faster
+        assert _ops.PATH_NAMES[_ops.select_path(4, 4096, 12288)] == "gemv"
         # Prefill shapes go to the tensor cores; ragged shapes to the masked kernel.
         assert name(2048, 24576, 4096) == "gemm_tc_pair"   # pairs of CTAs share the dequantised weights
         assert name(256, 24576, 4096) == "gemm_tc"
         assert name(128, 4096, 12288) == "gemm_tc_small"   # weights on the M side of the MMA
-        assert name(16, 24576, 4096) == "gemm_tc_small"
+        assert name(16, 24576, 4096) == "gemv"             # wide N, whole operand on chip: streaming still wins
+        assert name(17, 24576, 4096) == "gemm_tc_small"
+        assert name(16, 6144, 4096) == "gemm_tc_small"
         assert name(64, 24576, 4096) == "gemm_tc"          # wide N: 256-wide tiles fill the SMs
         # More than 128 rows on a shape whose 256 x 256 tiles would fill under half of the SMs: the
         # tensor-memory GEMM, which cuts K into slices (also the kernel for N % 256 == 128).
@@ -192,7 +195,8 @@ def test_dispatcher_choices_and_scratch_sizes():
         # small-M tensor-core GEMM: counters + one FP32 partial tile [M, 128] per row block and
         # slice of K; 32 row blocks are cut 8 ways, 192 row blocks 3 ways (waves of 2 * 148 CTAs)
         assert ws(16, 4096, 4096, _ops.PATH_AUTO) == 64 * 1024 + 32 * 8 * 16 * 128 * 4
-        assert ws(16, 24576, 4096, _ops.PATH_AUTO) == 64 * 1024 + 192 * 3 * 16 * 128 * 4
+        assert ws(17, 24576, 4096, _ops.PATH_AUTO) == 64 * 1024 + 192 * 3 * 17 * 128 * 4
+        assert ws(16, 24576, 4096, _ops.PATH_AUTO) == 0
         # tensor-memory GEMM: one FP32 partial tile [M, 256] per row block and slice (16 blocks cut 8 ways)
         assert ws(129, 4096, 12288, _ops.PATH_AUTO) == 64 * 1024 + 16 * 8 * 129 * 256 * 4
     finally:
