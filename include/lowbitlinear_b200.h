@@ -60,7 +60,8 @@ extern "C" {
                                       reference GEMM's operand policy, csrc/cute_w4a16_gemm.cu:160-162)
                                       also where the dispatcher would pick a streaming kernel, which
                                       keeps the FP32 scale: the any-shape operator then runs a
-                                      tensor-core or the masked kernel instead (slower for M <= 8)  */
+                                      tensor-core or the masked kernel instead (slower where it matters:
+                                      M <= 8, and M <= 16 on shapes with N >= 16384)  */
 
 #define LBL_FLAG_INDEPENDENT 4u    /* with LBL_FLAG_PDL: this call reads nothing that the previous kernel
                                       in the stream writes and writes nothing that it reads or writes,

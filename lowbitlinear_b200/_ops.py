@@ -147,7 +147,8 @@ def set_independent_launches(enabled):
 def set_reference_gemm_policy(enabled):
     """Make the any-shape operator round every dequantised weight to FP16 before the product on
     ALL shapes, as the reference GEMM does (``csrc/cute_w4a16_gemm.cu:160-162``).  By default the
-    shapes it hands to the streaming kernels (M <= 8, or M <= 32 with a ragged N; K % 256 == 0)
+    shapes it hands to the streaming kernels (M <= 8, M <= 16 when N >= 16384, or M <= 32 with a
+    ragged N; K % 256 == 0)
     keep the FP32 scale, which is closer to the FP32 reference path but differs from the
     reference GEMM's own outputs by up to an FP16 step; with this switch those shapes run a
     tensor-core or the masked kernel instead (slower)."""
